@@ -1,0 +1,118 @@
+"""Seeded test cases shared by the golden generator, the oracle tests and the GPU parity tests.
+
+Inputs are always drawn on the CPU generator in the order q, k, v, (dO) as fp32
+``randn`` (times ``std``), then cast -- the order the reference's own tests use
+(``tests/ops/test_flash_attn.py:24-31,43-63``).
+"""
+import numpy as np
+import torch
+
+DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+# max-abs tolerances on O, LSE, dQ, dK, dV against the reference
+TOL = {"fp32": 2e-3, "fp16": 1e-2, "bf16": 2e-2}
+# golden O / dQ / dK / dV tensors keep every ROWSTEP-th sequence row (row 0 included) to stay small
+ROWSTEP = 7
+
+
+def _c(B, Hq, Hkv, Sq, Sk, D, causal, dtype="fp32", seed=42, std=1.0, scale=None):
+    return dict(B=B, Hq=Hq, Hkv=Hkv, Sq=Sq, Sk=Sk, D=D, causal=causal, dtype=dtype, seed=seed, std=std, scale=scale)
+
+
+# The reference's forward matrix (heads x seq_lens x head_dim x causal, B=2, fp32, seed 42),
+# thinned to keep the fixture small, plus 16-bit and ragged / larger cases.
+FWD_CASES = {}
+for _hq, _hkv in ((8, 8), (8, 2), (8, 1)):
+    for _sq, _sk in ((32, 32), (16, 64), (64, 32)):
+        for _d in (64, 80, 96, 128, 256):
+            for _causal in (False, True):
+                if (_d in (80, 96, 256)) and (_hq, _hkv) != (8, 2):
+                    continue
+                FWD_CASES[f"ref_h{_hq}x{_hkv}_s{_sq}x{_sk}_d{_d}_c{int(_causal)}"] = _c(2, _hq, _hkv, _sq, _sk, _d, _causal)
+FWD_CASES.update({
+    "bf16_gqa_s200_d128_causal": _c(1, 4, 2, 200, 200, 128, True, "bf16", seed=7),
+    "fp16_mqa_s129x333_d128_causal": _c(1, 4, 1, 129, 333, 128, True, "fp16", seed=8),
+    "bf16_mha_s384_d128_causal": _c(1, 2, 2, 384, 384, 128, True, "bf16", seed=9),
+    "bf16_mha_s256x512_d128_full": _c(1, 2, 2, 256, 512, 128, False, "bf16", seed=10),
+    "fp16_gqa_s300x100_d128_causal": _c(1, 4, 2, 300, 100, 128, True, "fp16", seed=11),
+    "bf16_gqa_s257_d64_causal": _c(1, 4, 2, 257, 257, 64, True, "bf16", seed=12),
+    "fp32_s1_d64": _c(1, 2, 1, 1, 1, 64, True, "fp32", seed=13),
+    "fp32_scale_s70x90_d96": _c(1, 4, 4, 70, 90, 96, True, "fp32", seed=14, scale=0.2),
+})
+
+BWD_CASES = {}
+for _hq, _hkv in ((4, 4), (4, 2), (4, 1)):
+    for _causal in (False, True):
+        BWD_CASES[f"ref_h{_hq}x{_hkv}_c{int(_causal)}"] = _c(2, _hq, _hkv, 16, 16, 64, _causal)
+BWD_CASES.update({
+    "fp32_gqa_s40x72_d80_causal": _c(1, 4, 2, 40, 72, 80, True, "fp32", seed=21),
+    "fp32_s72x40_d128_causal": _c(1, 2, 1, 72, 40, 128, True, "fp32", seed=22),
+    "bf16_gqa_s200_d128_causal": _c(1, 4, 2, 200, 200, 128, True, "bf16", seed=23),
+    "fp16_mha_s256x384_d128_full": _c(1, 2, 2, 256, 384, 128, False, "fp16", seed=24),
+    "bf16_mqa_s130_d64_causal": _c(1, 4, 1, 130, 130, 64, True, "bf16", seed=25),
+    "fp32_d256_s33": _c(1, 2, 2, 33, 33, 256, True, "fp32", seed=26),
+})
+
+
+def _d(B, Hq, Hkv, Scap, D, dtype="fp32", seed=42, std=1.0, lens=None, scale=None):
+    return dict(B=B, Hq=Hq, Hkv=Hkv, Scap=Scap, D=D, dtype=dtype, seed=seed, std=std, lens=lens, scale=scale)
+
+
+DECODE_CASES = {}
+for _hq, _hkv in ((8, 8), (8, 2), (8, 1)):
+    for _kv in (32, 128, 512, 1024):
+        for _dd in (64, 128):
+            DECODE_CASES[f"ref_h{_hq}x{_hkv}_kv{_kv}_d{_dd}"] = _d(2, _hq, _hkv, _kv, _dd)
+DECODE_CASES.update({
+    "bf16_gqa_lens": _d(4, 32, 8, 2048, 128, "bf16", seed=31, lens=[2048, 1, 777, 1500]),
+    "fp16_mqa_g64": _d(2, 64, 1, 4096, 128, "fp16", seed=32, std=0.5),
+    "bf16_gqa_empty": _d(3, 8, 2, 300, 128, "bf16", seed=33, lens=[0, 300, 129]),
+    "fp32_d96_lens": _d(2, 4, 2, 200, 96, "fp32", seed=34, lens=[37, 200]),
+    "fp16_mha_d64": _d(2, 4, 4, 1000, 64, "fp16", seed=35, lens=[1000, 513]),
+})
+
+
+def _draw(shape, c):
+    return (torch.randn(*shape, dtype=torch.float32) * c["std"]).to(DT[c["dtype"]])
+
+
+def make_fwd_inputs(c):
+    torch.manual_seed(c["seed"])
+    q = _draw((c["B"], c["Hq"], c["Sq"], c["D"]), c)
+    k = _draw((c["B"], c["Hkv"], c["Sk"], c["D"]), c)
+    v = _draw((c["B"], c["Hkv"], c["Sk"], c["D"]), c)
+    return q, k, v
+
+
+def make_bwd_inputs(c):
+    q, k, v = make_fwd_inputs(c)
+    do = _draw((c["B"], c["Hq"], c["Sq"], c["D"]), c)
+    return q, k, v, do
+
+
+def make_decode_inputs(c):
+    torch.manual_seed(c["seed"])
+    q = _draw((c["B"], c["Hq"], 1, c["D"]), c)
+    k = _draw((c["B"], c["Hkv"], c["Scap"], c["D"]), c)
+    v = _draw((c["B"], c["Hkv"], c["Scap"], c["D"]), c)
+    lens = None if c["lens"] is None else torch.tensor(c["lens"], dtype=torch.int32)
+    return q, k, v, lens
+
+
+def config1_inputs():
+    """BASELINE config 1: fp32, B=2, H=8, S=512, D=64, seed 0."""
+    torch.manual_seed(0)
+    return tuple(torch.randn(2, 8, 512, 64, dtype=torch.float32) for _ in range(3))
+
+
+def input_checksum(*ts):
+    return float(sum(t.double().sum().item() for t in ts))
+
+
+def to_np(t):
+    """bf16 has no numpy dtype: store 16-bit results widened to fp32 (exact)."""
+    return t.float().numpy() if t.dtype != torch.float32 else t.numpy()
+
+
+def load_golden(name):
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name + ".npz"))

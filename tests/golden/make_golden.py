@@ -1,0 +1,94 @@
+"""Generate golden vectors from the UNMODIFIED reference (run in the build container only).
+
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [/path/to/reference]
+
+Imports ``stackkernels`` from the reference checkout, runs its CPU path
+(``attention_reference`` / ``flash_attention`` / ``flash_decode`` and autograd
+through them) on seeded inputs and writes ``tests/golden/*.npz``.  The reference
+checkout does not exist where the GPU tests run, which is why the outputs are
+committed.  Inputs are regenerated from the recorded seed by
+``tests/_cases.py``; each file also stores a checksum of its inputs so that a
+generator mismatch is detected rather than silently compared.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))          # tests/
+from _cases import (FWD_CASES, BWD_CASES, DECODE_CASES, make_fwd_inputs, make_bwd_inputs,  # noqa: E402
+                    make_decode_inputs, config1_inputs, input_checksum, to_np, ROWSTEP)
+
+ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+sys.path.insert(0, os.path.join(ref_root, "src"))
+os.environ.setdefault("STACKKERNELS_BACKEND", "reference")
+from stackkernels._reference.torch.attention import attention_reference  # noqa: E402
+from stackkernels.torch.attention import flash_attention, flash_decode   # noqa: E402
+
+
+def main():
+    torch.set_num_threads(8)
+    # ---- BASELINE config 1: full checksums + strided sample -------------------------------
+    q, k, v = config1_inputs()
+    o, lse = attention_reference(q, k, v, is_causal=True, sm_scale=0.125)
+    o_pub = flash_attention(q, k, v, is_causal=True, sm_scale=0.125)
+    assert torch.equal(o, o_pub)
+    np.savez_compressed(
+        os.path.join(HERE, "config1.npz"),
+        in_sum=input_checksum(q, k, v),
+        o_sum=o.double().sum().item(), o_abs=o.double().abs().sum().item(), lse_sum=lse.double().sum().item(),
+        o_sample=o[:, ::3, ::29, :].numpy(), lse_sample=lse[:, ::3, ::29].numpy(),
+        o_head=o[0, 0, 0, :4].numpy(), lse_head=lse[0, 0, :4].numpy())
+
+    # ---- forward cases ---------------------------------------------------------------------
+    out = {}
+    for name, c in FWD_CASES.items():
+        q, k, v = make_fwd_inputs(c)
+        o, lse = attention_reference(q, k, v, is_causal=c["causal"], sm_scale=c.get("scale"))
+        out[name + "/in_sum"] = input_checksum(q, k, v)
+        out[name + "/o"] = to_np(o[:, :, ::ROWSTEP])
+        out[name + "/lse"] = lse.numpy()
+    np.savez_compressed(os.path.join(HERE, "fwd.npz"), **out)
+
+    # ---- backward cases (autograd through the reference, as its CPU branch does) -----------
+    out = {}
+    for name, c in BWD_CASES.items():
+        q, k, v, do = make_bwd_inputs(c)
+        q1, k1, v1 = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+        o = flash_attention(q1, k1, v1, is_causal=c["causal"], sm_scale=c.get("scale"))
+        o.backward(do)
+        out[name + "/in_sum"] = input_checksum(q, k, v, do)
+        out[name + "/o"] = to_np(o.detach()[:, :, ::ROWSTEP])
+        out[name + "/dq"] = to_np(q1.grad[:, :, ::ROWSTEP])
+        out[name + "/dk"] = to_np(k1.grad[:, :, ::ROWSTEP])
+        out[name + "/dv"] = to_np(v1.grad[:, :, ::ROWSTEP])
+    np.savez_compressed(os.path.join(HERE, "bwd.npz"), **out)
+
+    # ---- decode cases (reference has no cache_seqlens: per-sequence slicing) ---------------
+    out = {}
+    for name, c in DECODE_CASES.items():
+        q, k, v, lens = make_decode_inputs(c)
+        if lens is None:
+            o = flash_decode(q, k, v, sm_scale=c.get("scale"))
+            _, lse = attention_reference(q, k, v, is_causal=False, sm_scale=c.get("scale"))
+        else:
+            os_, ls_ = [], []
+            for b in range(q.shape[0]):
+                n = int(lens[b])
+                ob, lb = attention_reference(q[b:b + 1], k[b:b + 1, :, :n], v[b:b + 1, :, :n],
+                                             is_causal=False, sm_scale=c.get("scale"))
+                os_.append(ob)
+                ls_.append(lb)
+            o, lse = torch.cat(os_), torch.cat(ls_)
+        out[name + "/in_sum"] = input_checksum(q, k, v)
+        out[name + "/o"] = to_np(o)
+        out[name + "/lse"] = lse.numpy()
+    np.savez_compressed(os.path.join(HERE, "decode.npz"), **out)
+    for f in ("config1", "fwd", "bwd", "decode"):
+        print(f, os.path.getsize(os.path.join(HERE, f + ".npz")), "bytes")
+
+
+if __name__ == "__main__":
+    main()

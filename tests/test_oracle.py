@@ -1,0 +1,85 @@
+"""CPU: the oracle restatement reproduces the stored outputs of the unmodified reference."""
+import numpy as np
+import pytest
+import torch
+
+from _cases import (FWD_CASES, BWD_CASES, DECODE_CASES, ROWSTEP, make_fwd_inputs, make_bwd_inputs,
+                    make_decode_inputs, config1_inputs, input_checksum, load_golden)
+from oracle import attention_oracle as orc
+
+# Oracle and reference run the same fp32 torch ops in a slightly different order.
+ORACLE_TOL = 2e-5
+
+
+def _close(a, b, tol=ORACLE_TOL):
+    a = torch.as_tensor(np.asarray(a)).float()
+    b = b.float()
+    assert a.shape == b.shape
+    fin = torch.isfinite(a)
+    assert torch.equal(fin, torch.isfinite(b))
+    assert torch.equal(a[~fin], b[~fin])
+    if fin.any():
+        assert (a[fin] - b[fin]).abs().max().item() <= tol
+
+
+def test_config1_checksums_match_reference():
+    g = load_golden("config1")
+    q, k, v = config1_inputs()
+    assert abs(input_checksum(q, k, v) - float(g["in_sum"])) < 1e-6
+    o, lse = orc.attention_forward(q, k, v, causal=True, scale=0.125)
+    # values recorded from the reference CPU path
+    assert abs(float(g["o_sum"]) - 100.40898935428527) < 1e-6
+    assert abs(float(g["lse_sum"]) - 47000.86151164025) < 1e-6
+    assert abs(o.double().sum().item() - float(g["o_sum"])) < 1e-2
+    assert abs(o.double().abs().sum().item() - float(g["o_abs"])) < 5e-2
+    assert abs(lse.double().sum().item() - float(g["lse_sum"])) < 1e-2
+    _close(g["o_sample"], o[:, ::3, ::29, :])
+    _close(g["lse_sample"], lse[:, ::3, ::29])
+    np.testing.assert_allclose(g["o_head"], [1.2335922718, -0.2971158922, -1.6723939180, -0.3838917017], atol=1e-6)
+
+
+@pytest.mark.parametrize("name", sorted(FWD_CASES))
+def test_forward_matches_reference(name):
+    c = FWD_CASES[name]
+    g = load_golden("fwd")
+    q, k, v = make_fwd_inputs(c)
+    assert abs(input_checksum(q, k, v) - float(g[name + "/in_sum"])) < 1e-6
+    o, lse = orc.attention_forward(q, k, v, causal=c["causal"], scale=c["scale"])
+    tol = ORACLE_TOL if c["dtype"] == "fp32" else 8e-3   # one 16-bit rounding of O
+    _close(g[name + "/o"], o[:, :, ::ROWSTEP], tol)
+    _close(g[name + "/lse"], lse)
+
+
+@pytest.mark.parametrize("name", sorted(BWD_CASES))
+def test_backward_matches_reference_autograd(name):
+    c = BWD_CASES[name]
+    g = load_golden("bwd")
+    q, k, v, do = make_bwd_inputs(c)
+    assert abs(input_checksum(q, k, v, do) - float(g[name + "/in_sum"])) < 1e-6
+    dq, dk, dv = orc.attention_backward(do, q, k, v, causal=c["causal"], scale=c["scale"])
+    tol = 1e-4 if c["dtype"] == "fp32" else 6e-2        # 16-bit grads: one rounding at |x| up to ~8
+    _close(g[name + "/dq"], dq[:, :, ::ROWSTEP], tol)
+    _close(g[name + "/dk"], dk[:, :, ::ROWSTEP], tol)
+    _close(g[name + "/dv"], dv[:, :, ::ROWSTEP], tol)
+
+
+@pytest.mark.parametrize("name", sorted(DECODE_CASES))
+def test_decode_matches_reference(name):
+    c = DECODE_CASES[name]
+    g = load_golden("decode")
+    q, k, v, lens = make_decode_inputs(c)
+    assert abs(input_checksum(q, k, v) - float(g[name + "/in_sum"])) < 1e-6
+    o, lse = orc.decode_forward(q, k, v, lens, scale=c["scale"])
+    tol = ORACLE_TOL if c["dtype"] == "fp32" else 8e-3
+    _close(g[name + "/o"], o, tol)
+    _close(g[name + "/lse"], lse)
+
+
+def test_sliced_evaluation_is_exact():
+    c = FWD_CASES["bf16_gqa_s200_d128_causal"]
+    q, k, v = make_fwd_inputs(c)
+    o, lse = orc.attention_forward(q, k, v, causal=True)
+    for b, h, os_, ls_ in orc.forward_sliced(q, k, v, causal=True):
+        g = q.shape[1] // k.shape[1]
+        assert torch.equal(os_[0], o[b, h * g:(h + 1) * g])
+        assert torch.allclose(ls_[0], lse[b, h * g:(h + 1) * g], atol=1e-6)
