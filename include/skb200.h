@@ -1,0 +1,114 @@
+/*
+ * skb200 -- C ABI of the B200 (sm_100a) attention hot path.
+ *
+ * The reference (stackformer-labs/Stackkernels) has no FFI: its seam is three Python
+ * launcher calls made by the torch frontend.  Each entry point below replaces one of
+ * them and is what a binding for this path binds.  File:line citations are relative
+ * to the reference checkout.
+ *
+ * Conventions
+ *   - All tensors are device pointers, contiguous, layout (B, H, S, D) row-major.
+ *   - dtype: SKB_F32 / SKB_F16 / SKB_BF16 for q, k, v, o, dO, dQ, dK, dV.  LSE is fp32.
+ *   - GQA/MQA: q head h reads kv head h / (Hq / Hkv).
+ *   - causal != 0 selects the bottom-right aligned mask: key j is visible to query i
+ *     iff j <= i + (Sk - Sq).  A row with no visible key yields O = 0, LSE = -inf.
+ *   - LSE is the natural-log logsumexp of scale * q.k over the visible keys.
+ *   - The library never allocates or frees device memory, never synchronises the
+ *     stream and keeps no state besides cached driver entry points.  Work is queued
+ *     on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream).
+ *   - Every function returns an skb_status; nothing is launched unless it is SKB_OK.
+ */
+#ifndef SKB200_H_
+#define SKB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum skb_dtype { SKB_F32 = 0, SKB_F16 = 1, SKB_BF16 = 2 } skb_dtype;
+
+typedef enum skb_status {
+  SKB_OK = 0,
+  SKB_ERR_NULL = 1,        /* a required pointer is NULL */
+  SKB_ERR_SHAPE = 2,       /* a dimension is < 1 (or Sq != 1 for decode) */
+  SKB_ERR_HEADS = 3,       /* Hq is not a multiple of Hkv */
+  SKB_ERR_HEAD_DIM = 4,    /* D unsupported: need 1 <= D <= 256 and D a multiple of 8 (16-bit) / 4 (fp32) */
+  SKB_ERR_DTYPE = 5,
+  SKB_ERR_ALIGN = 6,       /* a tensor pointer is not 16-byte aligned */
+  SKB_ERR_WORKSPACE = 7,   /* workspace missing or smaller than skb_*_workspace_bytes() */
+  SKB_ERR_CUDA = 8,        /* a CUDA runtime/driver call failed; see skb_last_cuda_error() */
+  SKB_ERR_UNSUPPORTED = 9, /* a specific implementation was forced for a shape it does not cover */
+  SKB_ERR_TOO_LARGE = 10   /* problem exceeds a fixed capacity of the entry point */
+} skb_status;
+
+/* Implementation selector (the `impl` argument). */
+enum {
+  SKB_IMPL_AUTO = 0,     /* tcgen05/TMA kernels where the shape qualifies, else the general kernels */
+  SKB_IMPL_GENERAL = 1,  /* fp32 CUDA-core kernels: any dtype, any D <= 256 */
+  SKB_IMPL_SM100 = 2     /* tensor-core kernels only; SKB_ERR_UNSUPPORTED if the shape does not qualify */
+};
+
+/* Prefill forward.  Replaces flash_attn_fwd(q, k, v, is_causal, sm_scale) -> (out, lse)
+ * (src/stackkernels/_core/attention/flash_fwd.py:182-264, called from
+ * src/stackkernels/torch/attention.py:43-49).
+ * q,o: (B,Hq,Sq,D)  k,v: (B,Hkv,Sk,D)  lse: (B,Hq,Sq) fp32. */
+int skb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                 int B, int Hq, int Hkv, int Sq, int Sk, int D,
+                 int dtype, int causal, float scale, int impl, void* stream);
+
+/* Bytes of scratch skb_attn_bwd needs (Delta = rowsum(dO*O), fp32 dQ accumulator for
+ * the tensor-core path).  Mirrors allocate_delta_buffer
+ * (src/stackkernels/_opt/memory/workspace.py:16-23). */
+size_t skb_attn_bwd_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype, int impl);
+
+/* Backward.  Replaces flash_attn_bwd(do, q, k, v, out, lse, is_causal, sm_scale) -> (dq, dk, dv)
+ * (src/stackkernels/_core/attention/flash_bwd.py:362-528, called from
+ * src/stackkernels/torch/attention.py:71-80).  dK/dV are accumulated by a single owner
+ * per KV tile (no atomics), summing over the query heads of the GQA group. */
+int skb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                 const float* lse, void* dq, void* dk, void* dv,
+                 int B, int Hq, int Hkv, int Sq, int Sk, int D,
+                 int dtype, int causal, float scale, int impl,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Split count the decode scheduler picks (>= 1) and the scratch it needs.
+ * Replaces the SPLIT_KV heuristic (src/stackkernels/_opt/classes/decode.py:23-29,
+ * src/stackkernels/_core/attention/decode.py:220-224) and allocate_split_kv_buffers
+ * (src/stackkernels/_opt/memory/workspace.py:26-45).  `sm_count` <= 0 means 148. */
+int skb_decode_num_splits(int B, int Hq, int Hkv, int Scap, int D, int dtype, int sm_count);
+size_t skb_decode_workspace_bytes(int B, int Hq, int Hkv, int Scap, int D, int dtype, int num_splits);
+
+/* Single-token decode over a KV cache.  Replaces core flash_decode(q, k, v, sm_scale) -> out
+ * (src/stackkernels/_core/attention/decode.py:192-312, called from
+ * src/stackkernels/torch/attention.py:152).
+ * q,o: (B,Hq,1,D)  k_cache,v_cache: (B,Hkv,Scap,D)  cache_seqlens: (B,) int32 or NULL
+ * (NULL = every sequence attends to all Scap rows, the reference behaviour; otherwise
+ * sequence b attends to rows [0, cache_seqlens[b]), values clamped to [0, Scap]).
+ * lse: (B,Hq) fp32 or NULL.  num_splits: value from skb_decode_num_splits, or 0 = pick. */
+int skb_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* cache_seqlens,
+               void* o, float* lse,
+               int B, int Hq, int Hkv, int Scap, int D,
+               int dtype, float scale, int num_splits, int impl,
+               void* workspace, size_t workspace_bytes, void* stream);
+
+/* Human-readable text for a status code; mirrors the messages of validate_attention_layout
+ * (src/stackkernels/_opt/memory/layout.py:19-39). */
+const char* skb_status_string(int status);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char* skb_last_cuda_error(void);
+/* Library ABI version (major*100 + minor). */
+int skb_version(void);
+/* Reads and clears the device-side status word (0 = ok).  Every wait inside the tensor-core
+ * kernels is bounded; one that gives up records (role << 16 | detail) here and the kernel
+ * returns instead of hanging.  Synchronises the device.  No counterpart in the reference. */
+int skb_device_status(unsigned int* status_out);
+/* 1 if prefill forward would take the tensor-core (tcgen05/TMA) path under SKB_IMPL_AUTO. */
+int skb_attn_fwd_uses_sm100(int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype, int causal);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SKB200_H_ */

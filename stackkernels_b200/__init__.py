@@ -1,0 +1,8 @@
+"""B200-native attention hot path (flash_attention fwd/bwd, flash_decode) behind the
+StackKernels PyTorch API.  Compute lives in ``libskb200.so`` (hand-written CUDA, sm_100a)."""
+from ._options import get_backend, options, set_backend
+from .attention import FlashAttention, FlashAttentionFunction, flash_attention, flash_decode
+
+__all__ = ["flash_attention", "flash_decode", "FlashAttention", "FlashAttentionFunction",
+           "get_backend", "set_backend", "options"]
+__version__ = "0.1.0"

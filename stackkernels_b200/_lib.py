@@ -1,0 +1,76 @@
+"""ctypes binding of ``libskb200.so`` (declared in ``include/skb200.h``).
+
+There is no fallback: if the shared library is missing or fails to load, every native
+call raises.  Nothing here routes to a CPU implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libskb200.so")
+
+SKB_F32, SKB_F16, SKB_BF16 = 0, 1, 2
+IMPL_AUTO, IMPL_GENERAL, IMPL_SM100 = 0, 1, 2
+IMPL_BY_NAME = {"auto": IMPL_AUTO, "general": IMPL_GENERAL, "sm100": IMPL_SM100}
+
+(SKB_OK, SKB_ERR_NULL, SKB_ERR_SHAPE, SKB_ERR_HEADS, SKB_ERR_HEAD_DIM, SKB_ERR_DTYPE, SKB_ERR_ALIGN,
+ SKB_ERR_WORKSPACE, SKB_ERR_CUDA, SKB_ERR_UNSUPPORTED, SKB_ERR_TOO_LARGE) = range(11)
+
+_c = ctypes
+_vp, _i, _f, _sz = _c.c_void_p, _c.c_int, _c.c_float, _c.c_size_t
+
+# name -> (restype, argtypes); every symbol include/skb200.h declares
+SIGNATURES = {
+    "skb_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "skb_attn_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i, _i]),
+    "skb_attn_bwd": (_i, [_vp] * 9 + [_i] * 6 + [_i, _i, _f, _i, _vp, _sz, _vp]),
+    "skb_decode_num_splits": (_i, [_i] * 7),
+    "skb_decode_workspace_bytes": (_sz, [_i] * 7),
+    "skb_decode": (_i, [_vp] * 6 + [_i] * 5 + [_i, _f, _i, _i, _vp, _sz, _vp]),
+    "skb_status_string": (_c.c_char_p, [_i]),
+    "skb_last_cuda_error": (_c.c_char_p, []),
+    "skb_version": (_i, []),
+    "skb_device_status": (_i, [_c.POINTER(_c.c_uint)]),
+    "skb_attn_fwd_uses_sm100": (_i, [_i] * 8),
+}
+
+_lib = None
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+def load():
+    """Load the library once; raise loudly when it is absent (no silent fallback)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise NativeLibraryError(
+            f"{LIB_PATH} not found: build it with `python -m stackkernels_b200.build` "
+            "(nvcc, sm_100a). The native attention path has no fallback.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)      # AttributeError here = header and library disagree
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+def status_string(code: int) -> str:
+    return load().skb_status_string(int(code)).decode()
+
+
+def last_cuda_error() -> str:
+    return load().skb_last_cuda_error().decode()
+
+
+def device_status() -> int:
+    v = ctypes.c_uint(0)
+    rc = load().skb_device_status(ctypes.byref(v))
+    if rc != SKB_OK:
+        raise NativeLibraryError(f"skb_device_status failed: {status_string(rc)} {last_cuda_error()}")
+    return int(v.value)

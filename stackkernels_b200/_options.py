@@ -1,0 +1,53 @@
+"""Global backend switch, same contract as the reference's ``stackkernels._options``
+(``src/stackkernels/_options.py:10-55``): ``STACKKERNELS_BACKEND`` environment variable,
+``set_backend`` / ``get_backend`` / ``options``.
+
+Values: ``auto`` (native kernels for CUDA tensors), ``native`` (always native; ``triton`` is
+accepted as an alias so existing configuration keeps working) and ``reference``.  The CPU
+reference implementation is not part of this package: with ``reference`` selected, or for a
+CPU tensor under ``auto``, the attention entry points raise instead of computing on the host.
+"""
+from __future__ import annotations
+
+import os
+
+VALID_BACKENDS = ("auto", "native", "triton", "reference")
+
+
+class Options:
+    def __init__(self, backend: str | None = None) -> None:
+        if backend is None:
+            backend = os.environ.get("STACKKERNELS_BACKEND", "auto")
+        self._backend = "auto"
+        self.backend = backend
+
+    @property
+    def backend(self) -> str:
+        return self._backend
+
+    @backend.setter
+    def backend(self, val: str) -> None:
+        normalized = str(val).strip().lower()
+        if normalized not in VALID_BACKENDS:
+            raise ValueError(f"Invalid backend '{val}'. Must be one of: {', '.join(VALID_BACKENDS)}")
+        self._backend = "native" if normalized == "triton" else normalized
+
+    def __repr__(self) -> str:
+        return f"Options(backend='{self._backend}')"
+
+
+_GLOBAL_OPTIONS = Options()
+
+
+def get_backend() -> str:
+    return _GLOBAL_OPTIONS.backend
+
+
+def set_backend(backend: str) -> None:
+    _GLOBAL_OPTIONS.backend = backend
+
+
+def options(backend: str | None = None) -> Options:
+    if backend is not None:
+        set_backend(backend)
+    return _GLOBAL_OPTIONS

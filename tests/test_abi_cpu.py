@@ -1,0 +1,118 @@
+"""CPU: the C-ABI library loads, exports every symbol the header declares, and rejects bad
+arguments on the host before any launch.  No compute is run here."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import stackkernels_b200 as skb
+from stackkernels_b200 import _lib, build
+from stackkernels_b200.launchers import validate_attention_layout
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.load()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "skb200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(skb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib):
+    names = _declared_symbols()
+    assert "skb_attn_fwd" in names and "skb_attn_bwd" in names and "skb_decode" in names
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(raw, n), f"{n} declared in skb200.h but not exported"
+    assert set(names) == set(_lib.SIGNATURES), "ctypes signatures and header disagree"
+
+
+def test_version_and_status_strings(lib):
+    assert lib.skb_version() >= 100
+    assert _lib.status_string(_lib.SKB_OK) == "ok"
+    assert "divisible" in _lib.status_string(_lib.SKB_ERR_HEADS)
+
+
+def test_argument_validation_happens_on_host(lib):
+    p = ctypes.c_void_p(1 << 20)   # never dereferenced: every call below must fail validation first
+    args = dict(B=1, Hq=4, Hkv=2, Sq=8, Sk=8, D=64, dt=_lib.SKB_F32)
+
+    def fwd(**kw):
+        a = {**args, **kw}
+        return lib.skb_attn_fwd(a.get("q", p), p, p, p, p, a["B"], a["Hq"], a["Hkv"], a["Sq"], a["Sk"], a["D"],
+                                a["dt"], 0, 0.125, a.get("impl", 0), None)
+    assert fwd(q=None) == _lib.SKB_ERR_NULL
+    assert fwd(Hq=3) == _lib.SKB_ERR_HEADS
+    assert fwd(D=66) == _lib.SKB_ERR_HEAD_DIM
+    assert fwd(D=512) == _lib.SKB_ERR_HEAD_DIM
+    assert fwd(Sq=0) == _lib.SKB_ERR_SHAPE
+    assert fwd(dt=7) == _lib.SKB_ERR_DTYPE
+    assert fwd(q=ctypes.c_void_p((1 << 20) + 4)) == _lib.SKB_ERR_ALIGN
+    assert fwd(impl=_lib.IMPL_SM100) == _lib.SKB_ERR_UNSUPPORTED     # fp32 has no tensor-core path
+    # backward without workspace, decode with too many splits
+    rc = lib.skb_attn_bwd(p, p, p, p, p, p, p, p, p, 1, 4, 2, 8, 8, 64, 0, 0, 0.125, 0, None, 0, None)
+    assert rc == _lib.SKB_ERR_WORKSPACE
+    rc = lib.skb_decode(p, p, p, None, p, None, 1, 4, 2, 65536, 64, 0, 0.125, 1000, 0, p, 1 << 30, None)
+    assert rc == _lib.SKB_ERR_TOO_LARGE
+
+
+def test_split_scheduler_and_workspace_sizes(lib):
+    # config 4 (B64 Hq32 Hkv8 cap 32768) and config 5 (B16 Hq64 Hkv1 131072)
+    s4 = lib.skb_decode_num_splits(64, 32, 8, 32768, 128, _lib.SKB_BF16, 148)
+    s5 = lib.skb_decode_num_splits(16, 64, 1, 131072, 128, _lib.SKB_F16, 148)
+    assert 1 <= s4 <= 256 and 1 <= s5 <= 256
+    assert 16 * s5 >= 148, "config 5 must produce enough work items to fill the SMs"
+    assert lib.skb_decode_num_splits(2, 8, 2, 32, 64, 0, 148) == 1
+    assert lib.skb_decode_num_splits(2, 8, 2, 128, 64, 0, 148) == 1
+    n = 64 * 32 * s4
+    assert lib.skb_decode_workspace_bytes(64, 32, 8, 32768, 128, _lib.SKB_BF16, s4) >= n * 128 * 4 + n * 8
+    assert lib.skb_attn_bwd_workspace_bytes(4, 64, 8, 8192, 8192, 128, _lib.SKB_BF16, 0) >= 4 * 64 * 8192 * 4
+
+
+def test_layout_validation_matches_reference_messages():
+    q = torch.zeros(2, 8, 4, 16)
+    with pytest.raises(ValueError, match="Expected 4D tensors"):
+        validate_attention_layout(q[0], q, q)
+    with pytest.raises(ValueError, match="Batch mismatch"):
+        validate_attention_layout(q, q[:1], q)
+    with pytest.raises(ValueError, match="head count mismatch"):
+        validate_attention_layout(q, q, q[:, :4])
+    with pytest.raises(ValueError, match="sequence length mismatch"):
+        validate_attention_layout(q, q, q[:, :, :2])
+    with pytest.raises(ValueError, match="Head dimension mismatch"):
+        validate_attention_layout(q, q[..., :8], q[..., :8])
+    with pytest.raises(ValueError, match="must be divisible"):
+        validate_attention_layout(q, q[:, :3], q[:, :3])
+    assert validate_attention_layout(q, q[:, :2], q[:, :2]) == (2, 8, 2, 4, 4, 16)
+
+
+def test_no_cpu_fallback_and_backend_switch():
+    q = torch.zeros(1, 2, 4, 8)
+    with pytest.raises(RuntimeError, match="CPU reference"):
+        skb.flash_attention(q, q, q)
+    with pytest.raises(RuntimeError, match="CPU reference"):
+        skb.flash_decode(q[:, :, :1], q, q)
+    assert skb.get_backend() == "auto"
+    skb.set_backend("triton")            # accepted alias of the native backend
+    assert skb.get_backend() == "native"
+    skb.set_backend("auto")
+    with pytest.raises(ValueError):
+        skb.set_backend("jax")
+
+
+def test_keyword_aliases():
+    from stackkernels_b200.attention import _merge_alias
+    assert _merge_alias(False, True, False, ("is_causal", "causal")) is True
+    assert _merge_alias(None, 0.5, None, ("sm_scale", "softmax_scale")) == 0.5
+    with pytest.raises(TypeError):
+        _merge_alias(0.25, 0.5, None, ("sm_scale", "softmax_scale"))
+    m = skb.FlashAttention(causal=True, softmax_scale=0.3)
+    assert m.is_causal is True and m.sm_scale == 0.3

@@ -1,0 +1,134 @@
+"""GPU parity: the CUDA path (through the C ABI) against the stored outputs of the unmodified
+reference and against the CPU oracle, on the same seeded inputs."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from _cases import (BWD_CASES, DECODE_CASES, FWD_CASES, ROWSTEP, config1_inputs, load_golden, make_bwd_inputs,
+                    make_decode_inputs, make_fwd_inputs)
+from _parity import assert_parity
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def skb():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import stackkernels_b200
+    from stackkernels_b200 import _lib
+    _lib.load()                      # fail loudly if the extension is missing
+    return stackkernels_b200
+
+
+def _impls_for(c):
+    impls = ["general"]
+    if c["dtype"] in ("fp16", "bf16") and c["D"] in (64, 128):
+        impls.append("sm100")
+    return impls
+
+
+def _check_status():
+    from stackkernels_b200 import _lib
+    assert _lib.device_status() == 0, "a bounded wait inside a kernel gave up"
+
+
+def test_config1_golden(skb):
+    from stackkernels_b200.launchers import flash_attn_fwd
+    g = load_golden("config1")
+    q, k, v = (t.cuda() for t in config1_inputs())
+    o, lse = flash_attn_fwd(q, k, v, is_causal=True, sm_scale=0.125)
+    o, lse = o.cpu(), lse.cpu()
+    assert_parity(o[:, ::3, ::29, :], g["o_sample"], "fp32", "O")
+    assert_parity(lse[:, ::3, ::29], g["lse_sample"], "fp32", "LSE")
+    n = o.numel()
+    assert abs(o.double().sum().item() - float(g["o_sum"])) < 2e-3 * math.sqrt(n)
+    assert abs(o.double().abs().sum().item() - float(g["o_abs"])) < 1e-4 * n
+    assert abs(lse.double().sum().item() - float(g["lse_sum"])) < 1e-4 * lse.numel()
+    o_pub = skb.flash_attention(q, k, v, causal=True, softmax_scale=0.125)
+    assert torch.equal(o_pub.cpu(), o)
+
+
+@pytest.mark.parametrize("name", sorted(FWD_CASES))
+def test_forward_vs_reference(skb, name):
+    from stackkernels_b200.launchers import flash_attn_fwd
+    c = FWD_CASES[name]
+    g = load_golden("fwd")
+    q, k, v = (t.cuda() for t in make_fwd_inputs(c))
+    for impl in _impls_for(c):
+        o, lse = flash_attn_fwd(q, k, v, is_causal=c["causal"], sm_scale=c["scale"], impl=impl)
+        torch.cuda.synchronize()
+        assert_parity(o[:, :, ::ROWSTEP], g[name + "/o"], c["dtype"], f"{name}[{impl}] O")
+        assert_parity(lse, g[name + "/lse"], c["dtype"], f"{name}[{impl}] LSE")
+    _check_status()
+
+
+@pytest.mark.parametrize("name", sorted(BWD_CASES))
+def test_backward_vs_reference_autograd(skb, name):
+    c = BWD_CASES[name]
+    g = load_golden("bwd")
+    q, k, v, do = (t.cuda() for t in make_bwd_inputs(c))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    o = skb.flash_attention(q, k, v, is_causal=c["causal"], sm_scale=c["scale"])
+    o.backward(do)
+    torch.cuda.synchronize()
+    assert_parity(o[:, :, ::ROWSTEP], g[name + "/o"], c["dtype"], f"{name} O")
+    assert_parity(q.grad[:, :, ::ROWSTEP], g[name + "/dq"], c["dtype"], f"{name} dQ")
+    assert_parity(k.grad[:, :, ::ROWSTEP], g[name + "/dk"], c["dtype"], f"{name} dK")
+    assert_parity(v.grad[:, :, ::ROWSTEP], g[name + "/dv"], c["dtype"], f"{name} dV")
+    _check_status()
+
+
+@pytest.mark.parametrize("name", sorted(DECODE_CASES))
+def test_decode_vs_reference(skb, name):
+    c = DECODE_CASES[name]
+    g = load_golden("decode")
+    q, k, v, lens = make_decode_inputs(c)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    lens_d = None if lens is None else lens.cuda()
+    for splits in (0, 1, 3):
+        from stackkernels_b200.launchers import flash_decode as core
+        o, lse = core(q, k, v, sm_scale=c["scale"], cache_seqlens=lens_d, return_lse=True, num_splits=splits)
+        torch.cuda.synchronize()
+        assert_parity(o, g[name + "/o"], c["dtype"], f"{name}[splits={splits}] O")
+        assert_parity(lse, g[name + "/lse"], c["dtype"], f"{name}[splits={splits}] LSE")
+    if lens is None:
+        o_pub = skb.flash_decode(q, k, v)                          # the reference's call form
+    else:
+        o_pub = skb.flash_decode(q, k_cache=k, v_cache=v, cache_seqlens=lens_d)
+    assert_parity(o_pub, g[name + "/o"], c["dtype"], f"{name} public")
+
+
+def test_reference_test_matrix_public_api(skb):
+    """The reference's own forward test (tests/ops/test_flash_attn.py:10-36): rtol=atol=1e-3, fp32."""
+    from oracle import attention_oracle as orc
+    for hq, hkv in ((8, 8), (8, 2), (8, 1)):
+        for sq, sk in ((32, 32), (16, 64), (64, 32)):
+            for d in (64, 80, 96, 128, 256):
+                for causal in (False, True):
+                    torch.manual_seed(42)
+                    q = torch.randn(2, hq, sq, d)
+                    k = torch.randn(2, hkv, sk, d)
+                    v = torch.randn(2, hkv, sk, d)
+                    out = skb.flash_attention(q.cuda(), k.cuda(), v.cuda(), is_causal=causal).cpu()
+                    exp, _ = orc.attention_forward(q, k, v, causal=causal)
+                    torch.testing.assert_close(out, exp, rtol=1e-3, atol=1e-3)
+
+
+def test_module_and_decode_start_pos(skb):
+    from oracle import attention_oracle as orc
+    torch.manual_seed(42)
+    q, k, v = torch.randn(1, 4, 16, 64), torch.randn(1, 2, 16, 64), torch.randn(1, 2, 16, 64)
+    out = skb.FlashAttention(is_causal=True)(q.cuda(), k.cuda(), v.cuda())
+    assert out.shape == q.shape and not torch.isnan(out).any()
+    # start_pos == S_k - 1 is the bottom-right causal shift of a one-row query
+    qd, kc, vc = torch.randn(2, 4, 1, 64), torch.randn(2, 2, 300, 64), torch.randn(2, 2, 300, 64)
+    o1 = skb.flash_decode(qd.cuda(), kc.cuda(), vc.cuda(), start_pos=199).cpu()
+    exp, _ = orc.attention_forward(qd, kc[:, :, :200], vc[:, :, :200], causal=True)
+    torch.testing.assert_close(o1, exp, rtol=1e-3, atol=1e-3)
+    with pytest.raises(AssertionError):
+        skb.flash_decode(q.cuda(), k.cuda(), v.cuda())            # q_len != 1
+    with pytest.raises(ValueError):
+        skb.flash_attention(q.cuda(), k.cuda()[:, :, :, :32], v.cuda())
