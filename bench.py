@@ -18,7 +18,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import time
 
@@ -30,6 +29,8 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     # name: (kind, params)
     "prefill_fwd_c2": ("fwd", dict(B=8, Hq=32, Hkv=32, S=4096, D=128, dtype="bf16", seed=1)),
+    # same kernel and tile shapes as config 2 on a quarter of the batch: the case ncu --set full captures
+    "prefill_fwd_profile": ("fwd", dict(B=2, Hq=32, Hkv=32, S=4096, D=128, dtype="bf16", seed=1)),
     "prefill_fwd_s8192": ("fwd", dict(B=4, Hq=64, Hkv=8, S=8192, D=128, dtype="bf16", seed=2)),
     "fwdbwd_c3": ("bwd", dict(B=4, Hq=64, Hkv=8, S=8192, D=128, dtype="bf16", seed=2)),
     "decode_c4": ("decode", dict(B=64, Hq=32, Hkv=8, cap=32768, D=128, dtype="bf16", seed=3, lens="uniform")),
@@ -48,48 +49,58 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons through NVML every few milliseconds while the timed
+    region runs (read-only queries; falls back to one nvidia-smi query if NVML is unavailable)."""
 
-    def __init__(self, gpu_index):
-        self.idx, self.proc = gpu_index, None
+    def __init__(self, gpu_index, period_s=0.004):
+        self.idx, self.period = gpu_index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop, self._thr, self._nv = False, None, None
+
+    def _loop(self):
+        nv, h = self._nv, self._h
+        bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown if hasattr(nv, "nvmlClocksEventReasonHwSlowdown")
+                else nv.nvmlClocksThrottleReasonHwSlowdown,
+                "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        while not self._stop:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for name, bit in bits.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.idx), "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml as nv
+            nv.nvmlInit()
+            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            phys = self.idx
+            if vis and all(x.strip().isdigit() for x in vis.split(",")):
+                phys = int(vis.split(",")[self.idx])
+            self._h = nv.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self._h, nv.NVML_CLOCK_SM)
+            self._nv = nv
+            import threading
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+        except Exception:
+            self._nv = None
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])), mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        # the busiest half of the samples is "under load" (the sampler also sees idle edges)
-        sm_sorted = sorted(sm)
-        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
-        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        if self._nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"], "samples": 0}
+        self._stop = True
+        self._thr.join(timeout=2)
+        sm = sorted(self.samples)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(sm)}
 
 
 def make_inputs(kind, p, device, pinned_host=False):
@@ -185,9 +196,12 @@ def run_native(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
         sampler = ClockSampler(local)
         sampler.start()
-        total_ms, per = time_steps(fn, steps, warmup)
+        total_ms, per = time_steps(fn, steps, 0)
         clocks = sampler.stop()
         if world > 1:
             dist.barrier()
@@ -208,7 +222,10 @@ def run_native(args):
                     out = flash_decode(dd[0], dd[1], dd[2], cache_seqlens=lens_d)
                 else:
                     raise NotImplementedError
-                return out.cpu()
+                out_host.copy_(out, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                return out_host
+            out_host = torch.empty(host[0].shape, dtype=host[0].dtype).pin_memory()
             for _ in range(2):
                 e2e_step()
             torch.cuda.synchronize()
@@ -230,14 +247,15 @@ def run_native(args):
         return res
 
     name = args.workload
-    r = measure(name, args.steps, args.warmup, with_e2e=True)
+    r = measure(name, args.steps, args.warmup, with_e2e=not args.no_e2e)
     kind, p = r["kind"], r["p"]
     is_decode = kind == "decode"
     scale = 1e-9 if is_decode else 1e-12
     unit = "GB/s" if is_decode else "TFLOP/s"
     value = world * r["units"] * scale / (r["ms_step"] * 1e-3)
     achieved = r["units"] * scale / (r["ms_kernel"] * 1e-3)
-    peak = peaks["hbm"] if is_decode else peaks["tf"]
+    long_region = r["ms_step"] * args.steps > 1000.0      # seconds-long loops run under the power cap
+    peak = peaks["hbm"] if is_decode else (peaks["tf_sus"] if long_region else peaks["tf"])
     line = {
         "metric": {"fwd": "attn_fwd_tflops", "bwd": "attn_bwd_tflops", "decode": "flash_decode_hbm_gbs"}[kind],
         "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -248,12 +266,14 @@ def run_native(args):
                    "l2": "inputs_exceed_l2"},
         "roofline": {"bound": "hbm" if is_decode else "tensor", "achieved": achieved, "peak": peak, "unit": unit,
                      "frac": achieved / peak, "traffic": None,
-                     "peak_source": f"{peaks['src']} ({'copy bandwidth' if is_decode else 'bf16 burst'})",
+                     "peak_source": f"{peaks['src']} ({'copy bandwidth' if is_decode else ('bf16 sustained' if long_region else 'bf16 burst')})",
+                     "frac_of_burst": None if is_decode else achieved / peaks["tf"],
                      "frac_of_sustained": None if is_decode else achieved / peaks["tf_sus"]},
         "clocks": r["clocks"], "gpu_launches": r["launches"],
-        "e2e": {"value": world * r["units"] * scale / r["e2e"]["s_step"], "unit": unit,
-                "h2d_bytes_per_step": r["e2e"]["h2d"], "d2h_bytes_per_step": r["e2e"]["d2h"]},
     }
+    if r["e2e"] is not None:
+        line["e2e"] = {"value": world * r["units"] * scale / r["e2e"]["s_step"], "unit": unit,
+                       "h2d_bytes_per_step": r["e2e"]["h2d"], "d2h_bytes_per_step": r["e2e"]["d2h"]}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(name, budget_s=args.cpu_seconds)
     if world == 1 and not args.no_extras:
@@ -359,6 +379,7 @@ def main():
     ap.add_argument("--workload", default="prefill_fwd_c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads reported under 'extras'")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "native":

@@ -5,6 +5,13 @@ A 16-bit result is itself rounded to 16 bits, as is the reference's; two correct
 nearly equal reals can differ by one unit in the last place, which exceeds the absolute bar
 once |x| > 2.56 (bf16) / 10.2 (fp16).  For such elements the allowance is one ulp
 (2^-7 |x| for bf16, 2^-10 |x| for fp16); everywhere else the absolute bar applies unchanged.
+
+dK / dV of a GQA/MQA group in 16 bits are a special case of the same effect: the reference's CPU
+path (autograd through ``repeat_interleave`` of a 16-bit tensor) rounds each query head's
+contribution to 16 bits and adds the G contributions in 16 bits, while the CUDA kernels -- like
+the reference's own GPU kernel -- accumulate the group in fp32 and round once.  Against the stored
+reference outputs those tensors get ``ulps=G``; against the oracle, which also rounds once, they
+get the normal one-ulp allowance.
 """
 import numpy as np
 import torch
@@ -23,7 +30,7 @@ def max_abs_err(ours, ref):
     return (a[fin] - b[fin]).abs().max().item()
 
 
-def assert_parity(ours, ref, dtype, what=""):
+def assert_parity(ours, ref, dtype, what="", ulps=1):
     a = ours.detach().float().cpu()
     b = torch.as_tensor(np.asarray(ref)).float() if not torch.is_tensor(ref) else ref.detach().float().cpu()
     assert a.shape == b.shape, f"{what}: shape {tuple(a.shape)} vs {tuple(b.shape)}"
@@ -32,6 +39,6 @@ def assert_parity(ours, ref, dtype, what=""):
     assert torch.equal(a[~fin], b[~fin]), f"{what}: infinities differ"
     if fin.any():
         err = (a[fin] - b[fin]).abs()
-        allowed = torch.clamp(b[fin].abs() * _ULP_REL[dtype], min=TOL[dtype])
+        allowed = torch.clamp(b[fin].abs() * (_ULP_REL[dtype] * ulps), min=TOL[dtype])
         worst = (err - allowed).max().item()
         assert worst <= 0, f"{what}: max abs err {err.max().item():.3e} (bar {TOL[dtype]:.0e}, dtype {dtype})"
