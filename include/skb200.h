@@ -94,6 +94,37 @@ int skb_decode(const void* q, const void* k_cache, const void* v_cache, const in
                int dtype, float scale, int num_splits, int impl,
                void* workspace, size_t workspace_bytes, void* stream);
 
+/* Decode for callers that must not allocate device memory.
+ *
+ * Some hosts of this library run where an allocation is off the table: an inference server whose
+ * memory was planned and handed out at start-up, a plugin whose enqueue hook is forbidden to call
+ * cudaMalloc, a latency-critical loop where cudaMalloc's implicit device synchronisation is not
+ * acceptable.  skb_decode needs split-KV scratch from its caller; this variant brings its own: a
+ * fixed array of SKB_DECODE_NOALLOC_SCRATCH_BYTES compiled into the library, so every GPU that
+ * loads the library holds that much memory until the process exits.  The call itself performs no
+ * cudaMalloc / cudaFree and calls no allocating routine.  Arguments and results are those of
+ * skb_decode without the workspace pair and the impl selector; inputs and outputs are still the
+ * caller's buffers.
+ *
+ *  - Limit: skb_decode_workspace_bytes(..., num_splits) must not exceed the built-in scratch,
+ *    otherwise SKB_ERR_TOO_LARGE is returned and nothing runs.  With num_splits == 0 the
+ *    scheduler's split count is lowered until the problem fits (SKB_ERR_TOO_LARGE if even one
+ *    split does not).
+ *  - The first call on each device looks up the scratch address (cudaGetSymbolAddress, with that
+ *    device current) and remembers it; make that first call before starting any stream capture.
+ *  - All calls on a device share the one scratch and it keeps whatever the last call left there.
+ *    Nothing in it needs clearing (each call overwrites every partial it later reads), but two
+ *    calls whose kernels overlap on the GPU -- different streams, or several host threads -- race
+ *    on it: keep calls to this entry point ordered on one stream per device.
+ *
+ * No counterpart in the reference, whose launcher allocates its partial buffers with torch.empty
+ * on every call. */
+#define SKB_DECODE_NOALLOC_SCRATCH_BYTES (16u << 20)
+int skb_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, const int32_t* cache_seqlens,
+                       void* o, float* lse,
+                       int B, int Hq, int Hkv, int Scap, int D,
+                       int dtype, float scale, int num_splits, void* stream);
+
 /* Human-readable text for a status code; mirrors the messages of validate_attention_layout
  * (src/stackkernels/_opt/memory/layout.py:19-39). */
 const char* skb_status_string(int status);

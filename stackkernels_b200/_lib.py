@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libskb200.so")
 
 SKB_F32, SKB_F16, SKB_BF16 = 0, 1, 2
 IMPL_AUTO, IMPL_GENERAL, IMPL_SM100 = 0, 1, 2
+DECODE_NOALLOC_SCRATCH_BYTES = 16 << 20
 IMPL_BY_NAME = {"auto": IMPL_AUTO, "general": IMPL_GENERAL, "sm100": IMPL_SM100}
 
 (SKB_OK, SKB_ERR_NULL, SKB_ERR_SHAPE, SKB_ERR_HEADS, SKB_ERR_HEAD_DIM, SKB_ERR_DTYPE, SKB_ERR_ALIGN,
@@ -29,6 +30,7 @@ SIGNATURES = {
     "skb_decode_num_splits": (_i, [_i] * 7),
     "skb_decode_workspace_bytes": (_sz, [_i] * 7),
     "skb_decode": (_i, [_vp] * 6 + [_i] * 5 + [_i, _f, _i, _i, _vp, _sz, _vp]),
+    "skb_decode_noalloc": (_i, [_vp] * 6 + [_i] * 5 + [_i, _f, _i, _vp]),
     "skb_status_string": (_c.c_char_p, [_i]),
     "skb_last_cuda_error": (_c.c_char_p, []),
     "skb_version": (_i, []),

@@ -190,6 +190,31 @@ int launch_fwd_sm100(const void* q, const void* k, const void* v, void* o, float
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// ------------------------------------------------------------------------------------ built-in decode scratch
+// Scratch for skb_decode_noalloc: lives in the library image, so every GPU that loads the
+// library carries these bytes until the process exits.  In host code the name below is only a
+// handle for the runtime, never a device address; the address a kernel may use comes from
+// cudaGetSymbolAddress, once per device, with that device current.
+static __device__ __align__(256) unsigned char g_decode_scratch[SKB_DECODE_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_decode_scratch_addr[kMaxDevices] = {};   // resolved device address per device ordinal
+
+int decode_scratch_for_current_device(void** out) {
+  int dev = -1;
+  SKB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return SKB_ERR_TOO_LARGE;
+  void* p = __atomic_load_n(&g_decode_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    // First use on this device.  Two host threads racing here resolve the same address.
+    SKB_CUDA(cudaGetSymbolAddress(&p, g_decode_scratch));
+    if (p == nullptr) return SKB_ERR_CUDA;
+    __atomic_store_n(&g_decode_scratch_addr[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return SKB_OK;
+}
+
 }  // namespace
 
 // =========================================================================================== C ABI
@@ -311,6 +336,37 @@ int skb_decode(const void* q, const void* k_cache, const void* v_cache, const in
   const size_t n = (size_t)B * Hq * num_splits;
   float* part_o = (float*)workspace;
   float2* part_ml = (float2*)((char*)workspace + align_up(n * D * sizeof(float), 256));
+  switch (dtype) {
+    case SKB_F32: return decode_general<float>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+    case SKB_F16: return decode_general<__half>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+    default: return decode_general<__nv_bfloat16>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+  }
+}
+
+int skb_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, const int32_t* cache_seqlens, void* o,
+                       float* lse, int B, int Hq, int Hkv, int Scap, int D, int dtype, float scale, int num_splits,
+                       void* stream) {
+  if (!q || !k_cache || !v_cache || !o) return SKB_ERR_NULL;
+  if (int rc = check_common(B, Hq, Hkv, 1, Scap, D, dtype)) return rc;
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o)) return SKB_ERR_ALIGN;
+  if (num_splits <= 0) {
+    // Scheduler's choice, lowered until the partial results fit the built-in scratch.
+    num_splits = skb_decode_num_splits(B, Hq, Hkv, Scap, D, dtype, 0);
+    while (num_splits > 1 &&
+           skb_decode_workspace_bytes(B, Hq, Hkv, Scap, D, dtype, num_splits) > SKB_DECODE_NOALLOC_SCRATCH_BYTES)
+      --num_splits;
+  }
+  if (num_splits > skb::general::kMaxSplits) return SKB_ERR_TOO_LARGE;
+  const size_t need = skb_decode_workspace_bytes(B, Hq, Hkv, Scap, D, dtype, num_splits);
+  if (need > SKB_DECODE_NOALLOC_SCRATCH_BYTES) return SKB_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  if (int rc = decode_scratch_for_current_device(&scratch)) return rc;
+  // Every (batch, head, split) partial is written by the split kernel before the combine kernel
+  // reads it, so nothing left in the scratch by an earlier call can leak into this one.
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t n = (size_t)B * Hq * num_splits;
+  float* part_o = (float*)scratch;
+  float2* part_ml = (float2*)((char*)scratch + align_up(n * D * sizeof(float), 256));
   switch (dtype) {
     case SKB_F32: return decode_general<float>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
     case SKB_F16: return decode_general<__half>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
