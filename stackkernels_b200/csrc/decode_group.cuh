@@ -1,0 +1,293 @@
+// Split-KV decode that serves a whole GQA/MQA group per CTA, so every K/V row is fetched from
+// HBM once however many query heads share it.  16-bit inputs, head dim 64 or 128, group <= 64.
+//
+// One CTA = (split, kv head, batch): a producer warp streams 64-row K and V tiles with TMA
+// (3-D tensor maps {D, capacity, B*Hkv}, 64x64 boxes, 128-byte swizzle, no multicast) through a
+// 3-stage shared-memory ring; four compute warps hold the group's query rows as the M dimension
+// of m16n8k16 tensor-core MMAs (heads padded to 16/32/64), read K with ldmatrix and V with
+// ldmatrix.trans from the swizzled tiles, and run an fp32 online softmax per warp.  Warps split
+// the 64 tile rows between them when the group needs fewer than four 16-row M tiles.  Partial
+// (O, max, sum) per (head, split) go to the same scratch layout as the general decode kernel and
+// are merged by decode_combine_kernel.
+//
+// Replaces _flash_decode_split_kernel (src/stackkernels/_core/attention/decode.py:15-121 in the
+// reference), which runs one program per query head and therefore re-reads a group's KV G times.
+#pragma once
+#include "sm100_ptx.cuh"
+
+namespace skb {
+namespace dgrp {
+
+constexpr int kTileN = 64;
+constexpr int kStages = 3;
+constexpr int kComputeWarps = 4;
+constexpr int kThreads = (kComputeWarps + 1) * 32;
+constexpr int kBoxBytes = kTileN * 128;   // 64 rows x 64 16-bit columns
+
+template <int HD> constexpr int tile_bytes() { return kBoxBytes * (HD / 64); }
+template <int HD> constexpr int smem_bytes() { return 1024 + kStages * 2 * tile_bytes<HD>() + 128; }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, __half) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, __nv_bfloat16) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, __half) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void bar_compute() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Byte offset of 16-byte chunk `ch` of row `row` inside a swizzled tile of HD columns.
+__device__ __forceinline__ uint32_t swz(int row, int ch) {
+  return (uint32_t)(ch >> 3) * kBoxBytes + (uint32_t)row * 128u + (uint32_t)(((ch & 7) ^ (row & 7)) << 4);
+}
+
+// MT = number of 16-row M tiles the group needs (1, 2 or 4).
+template <typename T, int HD, int MT>
+__global__ void __launch_bounds__(kThreads, 2)
+decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+              const T* __restrict__ q, const int32_t* __restrict__ seqlens, float* __restrict__ part_o,
+              float2* __restrict__ part_ml, int Hq, int Hkv, int Scap, int nsplit, float scale_log2) {
+  constexpr int TILE = tile_bytes<HD>();
+  constexpr int NP = kComputeWarps / MT;      // warps sharing one M tile split the tile's rows NP ways
+  constexpr int NW = kTileN / NP;             // tile rows per warp
+  constexpr int KS = HD / 16;                 // k-steps of QK^T
+  constexpr int NT_S = NW / 8;                // score n-tiles per warp
+  constexpr int NT_O = HD / 8;                // output n-tiles
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (sbase - ptx::smem_u32(smem_raw));
+  const uint32_t sBar = sbase + kStages * 2 * TILE;   // full[kStages], empty[kStages]
+  volatile int* s_abort = reinterpret_cast<volatile int*>(gbase + kStages * 2 * TILE + 64);
+  auto sK = [&](int st) -> uint32_t { return sbase + (uint32_t)st * 2u * TILE; };
+  auto sV = [&](int st) -> uint32_t { return sbase + (uint32_t)st * 2u * TILE + TILE; };
+  auto full = [&](int st) -> uint32_t { return sBar + 8u * st; };
+  auto empty = [&](int st) -> uint32_t { return sBar + 8u * (kStages + st); };
+
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int len = seqlens ? min(max(seqlens[b], 0), Scap) : Scap;
+  const int chunk = cdiv(cdiv(len, nsplit), kTileN) * kTileN;
+  const int start = split * chunk;
+  const int end = min(len, start + chunk);
+  const int ntiles = end > start ? cdiv(end - start, kTileN) : 0;
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full(s), 1);
+      ptx::mbar_init(empty(s), kComputeWarps);
+    }
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == kComputeWarps) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      ptx::prefetch_tmap(&tm_k);
+      ptx::prefetch_tmap(&tm_v);
+      bool ok = true;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int st = j % kStages;
+        ok = ptx::mbar_wait(empty(st), (uint32_t)((j / kStages) & 1) ^ 1u, s_abort);
+        if (!ok) break;
+        ptx::mbar_expect_tx(full(st), 2 * TILE);
+        const int row = start + j * kTileN;
+        for (int h = 0; h < HD / 64; ++h) {
+          ptx::tma_load_3d(sK(st) + h * kBoxBytes, &tm_k, h * 64, row, b * Hkv + hkv, full(st));
+          ptx::tma_load_3d(sV(st) + h * kBoxBytes, &tm_v, h * 64, row, b * Hkv + hkv, full(st));
+        }
+      }
+      if (!ok) atomicCAS(&g_dev_status, 0u, (4u << 16));
+    }
+    return;   // the producer warp takes no part in the compute-warp barriers below
+  }
+
+  // ------------------------------------------------------------------ compute warps
+  const int mt = warp % MT, part = warp / MT;
+  const int n0 = part * NW;
+  const int g = lane >> 2, tq = lane & 3;
+  const int mi = lane >> 3, ri = lane & 7;    // ldmatrix: lane -> (matrix, row)
+  const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
+
+  uint32_t qf[KS][4];
+  {
+    const T* qb = q + ((size_t)b * Hq + (size_t)hkv * G) * HD;
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+      const int c = 16 * kk + 2 * tq;
+      qf[kk][0] = r_lo < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * HD + c) : 0u;
+      qf[kk][1] = r_hi < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * HD + c) : 0u;
+      qf[kk][2] = r_lo < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * HD + c + 8) : 0u;
+      qf[kk][3] = r_hi < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * HD + c + 8) : 0u;
+    }
+  }
+  float oacc[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;   // l: this thread's share of the row sum
+  bool ok = true;
+
+  for (int j = 0; j < ntiles; ++j) {
+    const int st = j % kStages;
+    ok = ptx::mbar_wait(full(st), (uint32_t)(j / kStages) & 1u, s_abort);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    const uint32_t kt = sK(st), vt = sV(st);
+    const int valid = end - (start + j * kTileN);     // rows of this tile inside the sequence (>= 1)
+    if (valid < n0 + NW) {
+      // Rows past the sequence end hold whatever the cache contains; their probabilities are zero,
+      // but 0 * NaN would still poison O, so the V rows this warp reads are cleared first.
+      for (int idx = lane; idx < NW * (HD / 8); idx += 32) {
+        const int row = n0 + idx / (HD / 8), ch = idx % (HD / 8);
+        if (row >= valid)
+          *reinterpret_cast<uint4*>(gbase + (vt - sbase) + swz(row, ch)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncwarp();
+    }
+
+    float sacc[NT_S][4];
+#pragma unroll
+    for (int i = 0; i < NT_S; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+#pragma unroll
+    for (int nt2 = 0; nt2 < NT_S / 2; ++nt2) {
+      const int row = n0 + 16 * nt2 + 8 * (mi >> 1) + ri;
+#pragma unroll
+      for (int kk = 0; kk < KS; ++kk) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(kt + swz(row, 2 * kk + (mi & 1)), b0, b1, b2, b3);
+        mma16816(sacc[2 * nt2], qf[kk], b0, b1, T());
+        mma16816(sacc[2 * nt2 + 1], qf[kk], b2, b3, T());
+      }
+    }
+    // online softmax for rows r_lo (elements 0,1) and r_hi (elements 2,3)
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT_S; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = n0 + 8 * nt + 2 * tq + (e & 1);
+        const float s = col < valid ? sacc[nt][e] * scale_log2 : -INFINITY;
+        sacc[nt][e] = s;
+        if (e < 2) mx_lo = fmaxf(mx_lo, s); else mx_hi = fmaxf(mx_hi, s);
+      }
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float ms_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ms_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+    const float a_lo = ptx::ex2(m_lo - ms_lo), a_hi = ptx::ex2(m_hi - ms_hi);
+    m_lo = mn_lo; m_hi = mn_hi;
+    float rs_lo = 0.f, rs_hi = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT_S; ++nt) {
+      sacc[nt][0] = ptx::ex2(sacc[nt][0] - ms_lo);
+      sacc[nt][1] = ptx::ex2(sacc[nt][1] - ms_lo);
+      sacc[nt][2] = ptx::ex2(sacc[nt][2] - ms_hi);
+      sacc[nt][3] = ptx::ex2(sacc[nt][3] - ms_hi);
+      rs_lo += sacc[nt][0] + sacc[nt][1];
+      rs_hi += sacc[nt][2] + sacc[nt][3];
+    }
+    l_lo = l_lo * a_lo + rs_lo;
+    l_hi = l_hi * a_hi + rs_hi;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+      oacc[i][0] *= a_lo; oacc[i][1] *= a_lo;
+      oacc[i][2] *= a_hi; oacc[i][3] *= a_hi;
+    }
+    // O += P V : the score accumulators of two adjacent n-tiles are the A fragment of one k-step
+#pragma unroll
+    for (int ks = 0; ks < NW / 16; ++ks) {
+      uint32_t pa[4];
+      pa[0] = pack2(sacc[2 * ks][0], sacc[2 * ks][1], T());
+      pa[1] = pack2(sacc[2 * ks][2], sacc[2 * ks][3], T());
+      pa[2] = pack2(sacc[2 * ks + 1][0], sacc[2 * ks + 1][1], T());
+      pa[3] = pack2(sacc[2 * ks + 1][2], sacc[2 * ks + 1][3], T());
+      const int row = n0 + 16 * ks + 8 * (mi & 1) + ri;
+#pragma unroll
+      for (int nt2 = 0; nt2 < NT_O / 2; ++nt2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(vt + swz(row, 2 * nt2 + (mi >> 1)), b0, b1, b2, b3);
+        mma16816(oacc[2 * nt2], pa, b0, b1, T());
+        mma16816(oacc[2 * nt2 + 1], pa, b2, b3, T());
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(empty(st));
+  }
+  if (!ok && lane == 0) atomicCAS(&g_dev_status, 0u, (5u << 16) | (unsigned)warp);
+
+  // ------------------------------------------------------------------ merge the warps' partials
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  bar_compute();   // every compute warp is done with the tile ring: reuse it as the merge buffer
+  float* obuf = reinterpret_cast<float*>(gbase);                       // [4 warps][16 rows][HD]
+  float* mlbuf = obuf + kComputeWarps * 16 * HD;                       // [4 warps][16 rows][2]
+  {
+    float* ow = obuf + warp * 16 * HD;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+      const int c = 8 * i + 2 * tq;
+      *reinterpret_cast<float2*>(ow + g * HD + c) = make_float2(oacc[i][0], oacc[i][1]);
+      *reinterpret_cast<float2*>(ow + (g + 8) * HD + c) = make_float2(oacc[i][2], oacc[i][3]);
+    }
+    if (tq == 0) {
+      mlbuf[(warp * 16 + g) * 2] = m_lo;      mlbuf[(warp * 16 + g) * 2 + 1] = l_lo;
+      mlbuf[(warp * 16 + g + 8) * 2] = m_hi;  mlbuf[(warp * 16 + g + 8) * 2 + 1] = l_hi;
+    }
+  }
+  bar_compute();
+  const int tid = threadIdx.x;   // 0..127
+  for (int idx = tid; idx < MT * 16 * (HD / 4); idx += kComputeWarps * 32) {
+    const int hrow = idx / (HD / 4), c4 = (idx % (HD / 4)) * 4;
+    if (hrow >= G) continue;
+    const int tmt = hrow >> 4, r = hrow & 15;
+    float M = -INFINITY;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) M = fmaxf(M, mlbuf[((p * MT + tmt) * 16 + r) * 2]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float L = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {
+        const int w = p * MT + tmt;
+        const float wgt = ptx::ex2(mlbuf[(w * 16 + r) * 2] - M);
+        const float4 x = *reinterpret_cast<const float4*>(obuf + (w * 16 + r) * HD + c4);
+        acc.x += x.x * wgt; acc.y += x.y * wgt; acc.z += x.z * wgt; acc.w += x.w * wgt;
+        L += mlbuf[(w * 16 + r) * 2 + 1] * wgt;
+      }
+    }
+    const size_t pbase = ((size_t)b * Hq + (size_t)hkv * G + hrow) * nsplit + split;
+    *reinterpret_cast<float4*>(part_o + pbase * HD + c4) = acc;
+    if (c4 == 0) part_ml[pbase] = make_float2(M, L);
+  }
+}
+
+}  // namespace dgrp
+}  // namespace skb

@@ -23,9 +23,6 @@
 namespace skb {
 namespace sm100 {
 
-// Device status word: 0 = ok; otherwise (code << 16 | detail) of the first bounded wait that gave up.
-__device__ unsigned int g_dev_status;
-
 constexpr int kFwdThreads = 384;
 constexpr int kTileM = 128;        // query rows per MMA tile (= TMEM lanes)
 constexpr int kTileN = 128;        // kv rows per tile

@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstring>
 
+#include "decode_group.cuh"
 #include "fwd_sm100.cuh"
 #include "general_kernels.cuh"
 #include "skb200.h"
@@ -145,9 +146,9 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
-// (BH, S, D) 16-bit tensor viewed as a 3-D map {D, S, BH}; boxes of 64 columns x 128 rows, 128-byte swizzle,
+// (BH, S, D) 16-bit tensor viewed as a 3-D map {D, S, BH}; boxes of 64 columns x box_rows rows, 128-byte swizzle,
 // out-of-range rows read as zero.
-int make_map_3d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, size_t BH) {
+int make_map_3d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, size_t BH, int box_rows = 128) {
   EncodeTiledFn enc = get_encode_tiled();
   if (enc == nullptr) {
     snprintf(tl_cuda_err, sizeof(tl_cuda_err), "cuTensorMapEncodeTiled entry point not available");
@@ -155,7 +156,7 @@ int make_map_3d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, size
   }
   const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
   const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
-  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(map, dtype == SKB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -189,6 +190,42 @@ int launch_fwd_sm100(const void* q, const void* k, const void* v, void* o, float
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ------------------------------------------------------------------------------------ group decode
+bool decode_group_covers(int Hq, int Hkv, int D, int dtype) {
+  return (dtype == SKB_F16 || dtype == SKB_BF16) && (D == 64 || D == 128) && Hq / Hkv <= 64;
+}
+
+template <typename T, int HD, int MT>
+int launch_decode_group(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int32_t* lens, float* part_o,
+                        float2* part_ml, int B, int Hq, int Hkv, int Scap, int nsplit, float scale, cudaStream_t st) {
+  auto kern = dgrp::decode_kernel<T, HD, MT>;
+  constexpr size_t smem = dgrp::smem_bytes<HD>();
+  if (int rc = set_smem(kern, smem)) return rc;
+  kern<<<dim3(nsplit, Hkv, B), dgrp::kThreads, smem, st>>>(mk, mv, (const T*)q, lens, part_o, part_ml, Hq, Hkv, Scap,
+                                                          nsplit, scale * kLog2e);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
+template <typename T>
+int decode_group(const void* q, const void* kc, const void* vc, const int32_t* lens, void* o, float* lse, int B, int Hq,
+                 int Hkv, int Scap, int D, int nsplit, float scale, float* part_o, float2* part_ml, cudaStream_t st) {
+  CUtensorMap mk, mv;
+  const int dt = DtypeOf<T>::value;
+  if (int rc = make_map_3d(&mk, dt, kc, D, Scap, (size_t)B * Hkv, dgrp::kTileN)) return rc;
+  if (int rc = make_map_3d(&mv, dt, vc, D, Scap, (size_t)B * Hkv, dgrp::kTileN)) return rc;
+  const int G = Hq / Hkv;
+  int rc;
+#define SKB_DG(HD_, MT_) launch_decode_group<T, HD_, MT_>(mk, mv, q, lens, part_o, part_ml, B, Hq, Hkv, Scap, nsplit, scale, st)
+  if (D == 64) rc = G <= 16 ? SKB_DG(64, 1) : (G <= 32 ? SKB_DG(64, 2) : SKB_DG(64, 4));
+  else rc = G <= 16 ? SKB_DG(128, 1) : (G <= 32 ? SKB_DG(128, 2) : SKB_DG(128, 4));
+#undef SKB_DG
+  if (rc) return rc;
+  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, lse, D, nsplit);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
 
 // ------------------------------------------------------------------------------------ built-in decode scratch
 // Scratch for skb_decode_noalloc: lives in the library image, so every GPU that loads the
@@ -298,11 +335,11 @@ int skb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, 
 }
 
 int skb_decode_num_splits(int B, int Hq, int Hkv, int Scap, int D, int dtype, int sm_count) {
-  (void)D; (void)dtype; (void)Hkv;
-  if (B < 1 || Hq < 1 || Scap < 1) return 1;
+  if (B < 1 || Hq < 1 || Hkv < 1 || Scap < 1) return 1;
   if (sm_count <= 0) sm_count = 148;
   if (Scap <= 128) return 1;
-  const long long units = (long long)B * Hq;
+  // one CTA per (split, kv head) when the group kernel applies, per (split, q head) otherwise
+  const long long units = (long long)B * (decode_group_covers(Hq, Hkv, D, dtype) ? Hkv : Hq);
   long long by_fill = (4LL * sm_count + units - 1) / units;   // enough CTAs to fill the GPU a few times over
   long long by_len = Scap / 2048;                              // ~2K rows per split balances ragged lengths
   long long s = by_fill > by_len ? by_fill : by_len;
@@ -326,7 +363,8 @@ int skb_decode(const void* q, const void* k_cache, const void* v_cache, const in
   if (!q || !k_cache || !v_cache || !o) return SKB_ERR_NULL;
   if (int rc = check_common(B, Hq, Hkv, 1, Scap, D, dtype)) return rc;
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o)) return SKB_ERR_ALIGN;
-  if (impl == SKB_IMPL_SM100) return SKB_ERR_UNSUPPORTED;
+  const bool group_ok = decode_group_covers(Hq, Hkv, D, dtype);
+  if (impl == SKB_IMPL_SM100 && !group_ok) return SKB_ERR_UNSUPPORTED;
   if (num_splits <= 0) num_splits = skb_decode_num_splits(B, Hq, Hkv, Scap, D, dtype, 0);
   if (num_splits > skb::general::kMaxSplits) return SKB_ERR_TOO_LARGE;
   if (!workspace || !aligned16(workspace) ||
@@ -336,6 +374,11 @@ int skb_decode(const void* q, const void* k_cache, const void* v_cache, const in
   const size_t n = (size_t)B * Hq * num_splits;
   float* part_o = (float*)workspace;
   float2* part_ml = (float2*)((char*)workspace + align_up(n * D * sizeof(float), 256));
+  if (group_ok && impl != SKB_IMPL_GENERAL) {
+    if (dtype == SKB_F16)
+      return decode_group<__half>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+    return decode_group<__nv_bfloat16>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+  }
   switch (dtype) {
     case SKB_F32: return decode_general<float>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
     case SKB_F16: return decode_general<__half>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
@@ -379,8 +422,8 @@ int skb_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, 
 int skb_device_status(unsigned int* status_out) {
   if (!status_out) return SKB_ERR_NULL;
   unsigned int zero = 0;
-  SKB_CUDA(cudaMemcpyFromSymbol(status_out, skb::sm100::g_dev_status, sizeof(unsigned int)));
-  SKB_CUDA(cudaMemcpyToSymbol(skb::sm100::g_dev_status, &zero, sizeof(unsigned int)));
+  SKB_CUDA(cudaMemcpyFromSymbol(status_out, skb::g_dev_status, sizeof(unsigned int)));
+  SKB_CUDA(cudaMemcpyToSymbol(skb::g_dev_status, &zero, sizeof(unsigned int)));
   return SKB_OK;
 }
 

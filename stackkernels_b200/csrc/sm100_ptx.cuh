@@ -7,6 +7,10 @@
 #include "common.cuh"
 
 namespace skb {
+
+// Device status word: 0 = ok; otherwise (role << 16 | detail) of the first bounded wait that gave up.
+__device__ unsigned int g_dev_status;
+
 namespace ptx {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -96,12 +96,18 @@ def test_decode_vs_reference(skb, name):
     q, k, v, lens = make_decode_inputs(c)
     q, k, v = q.cuda(), k.cuda(), v.cuda()
     lens_d = None if lens is None else lens.cuda()
-    for splits in (0, 1, 3):
-        from stackkernels_b200.launchers import flash_decode as core
-        o, lse = core(q, k, v, sm_scale=c["scale"], cache_seqlens=lens_d, return_lse=True, num_splits=splits)
-        torch.cuda.synchronize()
-        assert_parity(o, g[name + "/o"], c["dtype"], f"{name}[splits={splits}] O")
-        assert_parity(lse, g[name + "/lse"], c["dtype"], f"{name}[splits={splits}] LSE")
+    from stackkernels_b200.launchers import flash_decode as core
+    impls = ["general"]
+    if c["dtype"] in ("fp16", "bf16") and c["D"] in (64, 128) and c["Hq"] // c["Hkv"] <= 64:
+        impls.append("sm100")          # the group-per-CTA tensor-core kernel
+    for impl in impls:
+        for splits in (0, 1, 3):
+            o, lse = core(q, k, v, sm_scale=c["scale"], cache_seqlens=lens_d, return_lse=True, num_splits=splits,
+                          impl=impl)
+            torch.cuda.synchronize()
+            assert_parity(o, g[name + "/o"], c["dtype"], f"{name}[{impl}, splits={splits}] O")
+            assert_parity(lse, g[name + "/lse"], c["dtype"], f"{name}[{impl}, splits={splits}] LSE")
+    _check_status()
     if lens is None:
         o_pub = skb.flash_decode(q, k, v)                          # the reference's call form
     else:
