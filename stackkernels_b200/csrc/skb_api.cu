@@ -8,6 +8,7 @@
 
 #include "decode_group.cuh"
 #include "fwd_sm100.cuh"
+#include "bwd_sm100.cuh"
 #include "general_kernels.cuh"
 #include "skb200.h"
 
@@ -149,6 +150,12 @@ EncodeTiledFn get_encode_tiled() {
 // (BH, S, D) 16-bit tensor viewed as a 3-D map {D, S, BH}; boxes of 64 columns x box_rows rows, 128-byte swizzle,
 // out-of-range rows read as zero.
 int make_map_3d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, size_t BH, int box_rows = 128) {
+  // The driver call below needs the device's primary context current on THIS host thread.  A thread
+  // that has only inherited a device ordinal (e.g. an autograd worker) may not have it bound yet;
+  // cudaSetDevice on the current ordinal binds it.
+  int dev = 0;
+  SKB_CUDA(cudaGetDevice(&dev));
+  SKB_CUDA(cudaSetDevice(dev));
   EncodeTiledFn enc = get_encode_tiled();
   if (enc == nullptr) {
     snprintf(tl_cuda_err, sizeof(tl_cuda_err), "cuTensorMapEncodeTiled entry point not available");
@@ -190,6 +197,57 @@ int launch_fwd_sm100(const void* q, const void* k, const void* v, void* o, float
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ------------------------------------------------------------------------------------ tensor-core backward
+bool bwd_sm100_covers(int D, int dtype) { return (dtype == SKB_F16 || dtype == SKB_BF16) && D == 128; }
+
+struct BwdWs {           // carve-up of the backward workspace for the tensor-core path
+  size_t delta_off, lse2_off, dq_off, total;
+};
+BwdWs bwd_sm100_ws(int B, int Hq, int Sq, int D) {
+  const size_t sq_pad = (size_t)cdiv(Sq, 128) * 128;
+  const size_t stats = align_up((size_t)B * Hq * sq_pad * sizeof(float), 256);
+  BwdWs w;
+  w.delta_off = 0;
+  w.lse2_off = stats;
+  w.dq_off = 2 * stats;
+  w.total = 2 * stats + align_up((size_t)B * Hq * Sq * D * sizeof(float), 256);
+  return w;
+}
+
+template <typename T>
+int launch_bwd_sm100(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                     void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk, int causal, float scale,
+                     void* workspace, cudaStream_t st) {
+  constexpr int D = 128;
+  const BwdWs w = bwd_sm100_ws(B, Hq, Sq, D);
+  float* delta = (float*)((char*)workspace + w.delta_off);
+  float* lse2 = (float*)((char*)workspace + w.lse2_off);
+  float* dq_acc = (float*)((char*)workspace + w.dq_off);
+  const int sq_pad = cdiv(Sq, 128) * 128;
+  const size_t bh = (size_t)B * Hq;
+  CUtensorMap mq, mk, mv, mdo;
+  const int dt = DtypeOf<T>::value;
+  if (int rc = make_map_3d(&mq, dt, q, D, Sq, bh)) return rc;
+  if (int rc = make_map_3d(&mdo, dt, dout, D, Sq, bh)) return rc;
+  if (int rc = make_map_3d(&mk, dt, k, D, Sk, (size_t)B * Hkv)) return rc;
+  if (int rc = make_map_3d(&mv, dt, v, D, Sk, (size_t)B * Hkv)) return rc;
+
+  const size_t prows = bh * sq_pad;
+  sm100::bwd_prep_kernel<T><<<(unsigned)((prows + 7) / 8), 256, 0, st>>>((const T*)dout, (const T*)o, lse, delta, lse2,
+                                                                        Sq, sq_pad, D, bh);
+  SKB_CUDA(cudaGetLastError());
+  SKB_CUDA(cudaMemsetAsync(dq_acc, 0, bh * Sq * D * sizeof(float), st));
+  auto kern = sm100::bwd_kernel<T>;
+  if (int rc = set_smem(kern, sm100::kBwdSmemBytes)) return rc;
+  kern<<<dim3(cdiv(Sk, 128), Hkv, B), sm100::kBwdThreads, sm100::kBwdSmemBytes, st>>>(
+      mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)dk, (T*)dv, Hq, Hkv, Sq, Sk, sq_pad, causal, scale, scale * kLog2e);
+  SKB_CUDA(cudaGetLastError());
+  const size_t n4 = bh * Sq * D / 4;
+  sm100::bwd_post_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_acc, (T*)dq, scale, n4);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
 
 // ------------------------------------------------------------------------------------ group decode
 bool decode_group_covers(int Hq, int Hkv, int D, int dtype) {
@@ -308,9 +366,14 @@ int skb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
 }
 
 size_t skb_attn_bwd_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype, int impl) {
-  (void)Hkv; (void)Sk; (void)D; (void)dtype; (void)impl;
-  if (B < 1 || Hq < 1 || Sq < 1) return 0;
-  return align_up((size_t)B * Hq * Sq * sizeof(float), 256);
+  (void)Hkv; (void)Sk;
+  if (B < 1 || Hq < 1 || Sq < 1 || D < 1) return 0;
+  const size_t general = align_up((size_t)B * Hq * Sq * sizeof(float), 256);
+  if (impl != SKB_IMPL_GENERAL && bwd_sm100_covers(D, dtype)) {
+    const size_t tc = bwd_sm100_ws(B, Hq, Sq, D).total;
+    return tc > general ? tc : general;
+  }
+  return general;
 }
 
 int skb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
@@ -321,11 +384,17 @@ int skb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, 
   if (!aligned16(dout) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dq) ||
       !aligned16(dk) || !aligned16(dv))
     return SKB_ERR_ALIGN;
-  if (impl == SKB_IMPL_SM100) return SKB_ERR_UNSUPPORTED;
+  const bool covers = bwd_sm100_covers(D, dtype);
+  if (impl == SKB_IMPL_SM100 && !covers) return SKB_ERR_UNSUPPORTED;
   if (!workspace || !aligned16(workspace) ||
       workspace_bytes < skb_attn_bwd_workspace_bytes(B, Hq, Hkv, Sq, Sk, D, dtype, impl))
     return SKB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
+  if (impl == SKB_IMPL_SM100 || (impl == SKB_IMPL_AUTO && covers && Sq >= 128 && Sk >= 128)) {
+    if (dtype == SKB_F16)
+      return launch_bwd_sm100<__half>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, causal, scale, workspace, st);
+    return launch_bwd_sm100<__nv_bfloat16>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, causal, scale, workspace, st);
+  }
   float* delta = (float*)workspace;
   switch (dtype) {
     case SKB_F32: return bwd_general<float>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);

@@ -115,6 +115,42 @@ def test_decode_vs_reference(skb, name):
     assert_parity(o_pub, g[name + "/o"], c["dtype"], f"{name} public")
 
 
+# shapes for the tensor-core backward (16-bit, D=128) checked against the oracle: ragged tails, S_q != S_k
+# in both directions (incl. fully masked query rows), MQA/GQA/MHA, causal and full
+TC_BWD_CASES = {
+    "bf16_gqa_s300_causal": dict(B=1, Hq=4, Hkv=2, Sq=300, Sk=300, causal=True, dtype="bf16", seed=51),
+    "fp16_mqa_s129x333_causal": dict(B=1, Hq=4, Hkv=1, Sq=129, Sk=333, causal=True, dtype="fp16", seed=52),
+    "bf16_mha_s384x128_causal": dict(B=1, Hq=2, Hkv=2, Sq=384, Sk=128, causal=True, dtype="bf16", seed=53),
+    "bf16_mha_s256x512_full": dict(B=2, Hq=2, Hkv=2, Sq=256, Sk=512, causal=False, dtype="bf16", seed=54),
+    "fp16_gqa_s640_causal": dict(B=1, Hq=8, Hkv=2, Sq=640, Sk=640, causal=True, dtype="fp16", seed=55),
+    "bf16_gqa_s128_causal": dict(B=2, Hq=4, Hkv=2, Sq=128, Sk=128, causal=True, dtype="bf16", seed=56),
+}
+
+
+@pytest.mark.parametrize("name", sorted(TC_BWD_CASES))
+def test_tensor_core_backward_vs_oracle(skb, name):
+    from _cases import DT
+    from oracle import attention_oracle as orc
+    from stackkernels_b200.launchers import flash_attn_bwd, flash_attn_fwd
+    c = TC_BWD_CASES[name]
+    torch.manual_seed(c["seed"])
+    dt = DT[c["dtype"]]
+    q = torch.randn(c["B"], c["Hq"], c["Sq"], 128).to(dt)
+    k = torch.randn(c["B"], c["Hkv"], c["Sk"], 128).to(dt)
+    v = torch.randn(c["B"], c["Hkv"], c["Sk"], 128).to(dt)
+    do = torch.randn(c["B"], c["Hq"], c["Sq"], 128).to(dt)
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    o, lse = flash_attn_fwd(qd, kd, vd, is_causal=c["causal"])
+    edq, edk, edv = orc.attention_backward(do, q, k, v, causal=c["causal"])
+    for impl in ("general", "sm100"):
+        dq, dk, dv = flash_attn_bwd(dod, qd, kd, vd, o, lse, is_causal=c["causal"], impl=impl)
+        torch.cuda.synchronize()
+        assert_parity(dq, edq, c["dtype"], f"{name}[{impl}] dQ")
+        assert_parity(dk, edk, c["dtype"], f"{name}[{impl}] dK")
+        assert_parity(dv, edv, c["dtype"], f"{name}[{impl}] dV")
+    _check_status()
+
+
 def test_reference_test_matrix_public_api(skb):
     """The reference's own forward test (tests/ops/test_flash_attn.py:10-36): rtol=atol=1e-3, fp32."""
     from oracle import attention_oracle as orc
