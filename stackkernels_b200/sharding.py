@@ -1,0 +1,108 @@
+"""Multi-GPU partition of the attention path: one process per GPU, no exchange step.
+
+A unit is one (batch, kv head) together with the H_q/H_kv query heads that read it.  Forward,
+backward (dK/dV sum only over the unit's own query heads) and decode never couple two units, so
+each rank takes a contiguous, batch-major range of units and computes it alone.  The only
+communication is an optional ``all_gather`` of results for validation; there is no collective on
+the data path.  The reference has no multi-device code at all; this module is what drives the
+kernels of this package across the GPUs of one box.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+Segment = Tuple[int, int, int]       # (batch index, first kv head, one past the last kv head)
+
+
+def partition_units(batch: int, kv_heads: int, world: int,
+                    batch_weights: Optional[Sequence[float]] = None) -> List[Tuple[int, int]]:
+    """Split the ``batch * kv_heads`` units into ``world`` contiguous ranges ``[start, end)``.
+
+    Units are numbered batch-major (``unit = b * kv_heads + h``).  With ``batch_weights`` (e.g. the
+    cached sequence lengths of a ragged decode batch) ranges are balanced by weight instead of by
+    count: rank r ends at the first unit where the running weight reaches ``(r+1)/world`` of the total.
+    """
+    n = batch * kv_heads
+    if world < 1:
+        raise ValueError("world must be >= 1")
+    if batch_weights is None:
+        bounds = [round(n * r / world) for r in range(world + 1)]
+    else:
+        if len(batch_weights) != batch:
+            raise ValueError(f"batch_weights must have {batch} entries")
+        w = [float(batch_weights[u // kv_heads]) for u in range(n)]
+        total = sum(w)
+        bounds, acc, u = [0], 0.0, 0
+        for r in range(1, world):
+            target = total * r / world
+            while u < n and acc + w[u] / 2 < target:
+                acc += w[u]
+                u += 1
+            bounds.append(u)
+        bounds.append(n)
+    return [(bounds[r], bounds[r + 1]) for r in range(world)]
+
+
+def segments_of(unit_range: Tuple[int, int], kv_heads: int) -> List[Segment]:
+    """Contiguous unit range -> per-batch segments ``(b, h0, h1)`` (each a slice of one batch row)."""
+    start, end = unit_range
+    segs: List[Segment] = []
+    u = start
+    while u < end:
+        b, h0 = divmod(u, kv_heads)
+        h1 = min(kv_heads, h0 + (end - u))
+        segs.append((b, h0, h1))
+        u += h1 - h0
+    return segs
+
+
+def slice_qkv(q, k, v, seg: Segment):
+    """Views of q, k, v (and anything shaped like q) that belong to one segment."""
+    b, h0, h1 = seg
+    g = q.shape[1] // k.shape[1]
+    return q[b:b + 1, h0 * g:h1 * g], k[b:b + 1, h0:h1], v[b:b + 1, h0:h1]
+
+
+def run_sharded(fn: Callable, q, k, v, rank: int, world: int, batch_weights=None):
+    """Apply ``fn(q_seg, k_seg, v_seg, seg) -> tuple of tensors`` to this rank's segments.
+
+    Returns ``[(seg, outputs), ...]``.  No communication happens here.
+    """
+    ranges = partition_units(q.shape[0], k.shape[1], world, batch_weights)
+    out = []
+    for seg in segments_of(ranges[rank], k.shape[1]):
+        qs, ks, vs = slice_qkv(q, k, v, seg)
+        res = fn(qs, ks, vs, seg)
+        out.append((seg, res if isinstance(res, tuple) else (res,)))
+    return out
+
+
+def gather_for_validation(local, templates: Sequence[torch.Tensor], q_heads: int, kv_heads: int,
+                          group=None) -> List[torch.Tensor]:
+    """Reassemble full tensors from every rank's segments (validation only, outside any timing).
+
+    ``local`` is the list returned by ``run_sharded``; ``templates`` give shape/dtype/device of the
+    full outputs (dim 0 = batch, dim 1 = heads; a template with ``kv_heads`` heads is filled with
+    kv-head slices, any other with the group's query heads).  Uses one ``all_gather_object`` of
+    CPU copies: simple and backend-agnostic (NCCL and Gloo both carry it).
+    """
+    g = q_heads // kv_heads
+    payload = [(seg, [t.detach().cpu() for t in outs]) for seg, outs in local]
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    gathered = [None] * world
+    if world > 1:
+        dist.all_gather_object(gathered, payload, group=group)
+    else:
+        gathered = [payload]
+    full = [torch.zeros(t.shape, dtype=t.dtype) for t in templates]
+    for part in gathered:
+        for (b, h0, h1), outs in part:
+            for dst, src in zip(full, outs):
+                if dst.shape[1] == kv_heads and kv_heads != q_heads:
+                    dst[b:b + 1, h0:h1] = src
+                else:
+                    dst[b:b + 1, h0 * g:h1 * g] = src
+    return full

@@ -1,0 +1,62 @@
+"""GPU (needs >= 2 devices, skipped otherwise): two ranks, one per GPU, each runs the CUDA kernels on its
+own (batch, kv-head) units; results are gathered over NCCL for validation only and checked against the oracle."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, result_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from oracle import attention_oracle as orc
+        from stackkernels_b200.launchers import flash_attn_bwd, flash_attn_fwd
+        from stackkernels_b200.sharding import gather_for_validation, run_sharded
+        torch.manual_seed(5)
+        B, Hq, Hkv, S, D = 2, 8, 4, 384, 128
+        q, do = torch.randn(B, Hq, S, D).bfloat16(), torch.randn(B, Hq, S, D).bfloat16()
+        k, v = torch.randn(B, Hkv, S, D).bfloat16(), torch.randn(B, Hkv, S, D).bfloat16()
+        g = Hq // Hkv
+
+        def fwd_bwd(qs, ks, vs, seg):
+            b, h0, h1 = seg
+            qd, kd, vd = qs.cuda(), ks.cuda(), vs.cuda()
+            o, lse = flash_attn_fwd(qd, kd, vd, is_causal=True)
+            dq, dk, dv = flash_attn_bwd(do[b:b + 1, h0 * g:h1 * g].cuda(), qd, kd, vd, o, lse, is_causal=True)
+            return o, lse, dq, dk, dv
+
+        local = run_sharded(fwd_bwd, q, k, v, rank, world)
+        torch.cuda.synchronize()
+        full = gather_for_validation(local, [q, torch.empty(B, Hq, S), q, k, v], Hq, Hkv)
+        if rank == 0:
+            o, lse = orc.attention_forward(q, k, v, causal=True)
+            dq, dk, dv = orc.attention_backward(do, q, k, v, causal=True)
+            for name, got, exp in zip(("O", "LSE", "dQ", "dK", "dV"), full, (o, lse, dq, dk, dv)):
+                err = (got.float() - exp.float()).abs().max().item()
+                assert err <= 4e-2, f"{name}: {err}"
+        dist.barrier()
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpus_shard_and_gather(tmp_path):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import torch.multiprocessing as mp
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    os.environ["PYTHONPATH"] = root + os.pathsep + os.environ.get("PYTHONPATH", "")
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]

@@ -1,0 +1,83 @@
+"""CPU, world_size 2 over Gloo: the multi-GPU host logic -- unit partition, per-rank slicing and the
+validation gather -- with the CPU oracle standing in for the kernels (which need a GPU)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from stackkernels_b200.sharding import partition_units, segments_of
+
+
+def test_partition_covers_every_unit_once():
+    for B, H, W in ((8, 32, 8), (4, 8, 8), (64, 8, 8), (16, 1, 8), (3, 5, 4), (1, 1, 2), (2, 3, 1)):
+        ranges = partition_units(B, H, W)
+        assert ranges[0][0] == 0 and ranges[-1][1] == B * H
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+        sizes = [e - s for s, e in ranges]
+        assert max(sizes) - min(sizes) <= 1
+        units = [u for r in ranges for (b, h0, h1) in segments_of(r, H) for u in range(b * H + h0, b * H + h1)]
+        assert units == list(range(B * H))
+
+
+def test_partition_balances_ragged_decode_batches_by_length():
+    torch.manual_seed(3)
+    lens = torch.randint(16384, 32769, (64,)).tolist()
+    ranges = partition_units(64, 8, 8, batch_weights=lens)
+    loads = [sum(lens[u // 8] for u in range(s, e)) for s, e in ranges]
+    assert ranges[-1][1] == 512 and max(loads) / (sum(loads) / 8) < 1.03
+    by_count = partition_units(64, 8, 8)
+    loads_c = [sum(lens[u // 8] for u in range(s, e)) for s, e in by_count]
+    assert max(loads) <= max(loads_c)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import attention_oracle as orc
+        from stackkernels_b200.sharding import gather_for_validation, run_sharded
+        torch.manual_seed(11)                                   # same inputs on every rank
+        B, Hq, Hkv, S, D = 3, 6, 3, 40, 16
+        q, do = torch.randn(B, Hq, S, D), torch.randn(B, Hq, S, D)
+        k, v = torch.randn(B, Hkv, S, D), torch.randn(B, Hkv, S, D)
+        g = Hq // Hkv
+
+        def fwd_bwd(qs, ks, vs, seg):
+            b, h0, h1 = seg
+            o, lse = orc.attention_forward(qs, ks, vs, causal=True)
+            dq, dk, dv = orc.attention_backward(do[b:b + 1, h0 * g:h1 * g], qs, ks, vs, causal=True)
+            return o, lse, dq, dk, dv
+
+        local = run_sharded(fwd_bwd, q, k, v, rank, world)
+        lse_t = torch.empty(B, Hq, S)
+        full = gather_for_validation(local, [q, lse_t, q, k, v], Hq, Hkv)
+        dist.barrier()
+        if rank == 0:
+            o, lse = orc.attention_forward(q, k, v, causal=True)
+            dq, dk, dv = orc.attention_backward(do, q, k, v, causal=True)
+            for got, exp in zip(full, (o, lse, dq, dk, dv)):
+                torch.testing.assert_close(got, exp, rtol=1e-5, atol=1e-5)
+            # the slowest-rank reduction the benchmark uses for its timing
+        t = torch.tensor([float(rank + 1)])
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        assert t.item() == world
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_shard_compute_and_gather(tmp_path):
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    os.environ["PYTHONPATH"] = root + os.pathsep + os.environ.get("PYTHONPATH", "")
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
