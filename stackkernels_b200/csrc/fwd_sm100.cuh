@@ -60,6 +60,19 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Optional timeline tracing for kernel development (compile with -DSKB_TRACE): CTA (0,0,0) records
+// clock64() at the phase boundaries of its MMA issuer and of one thread per softmax warpgroup.
+#ifdef SKB_TRACE
+__device__ long long g_trace[3 * 4096];
+#define SKB_TR(role, idx, ev)                                                                   \
+  do {                                                                                          \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 340)                     \
+      g_trace[(role) * 4096 + (idx) * 12 + (ev)] = clock64();                                   \
+  } while (0)
+#else
+#define SKB_TR(role, idx, ev) do {} while (0)
+#endif
+
 template <typename T, int HD>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -185,12 +198,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const int st = j % kStages, stn = (j + 1) % kStages;
         const uint32_t ph = (uint32_t)(j / kStages) & 1u, phn = (uint32_t)((j + 1) / kStages) & 1u;
         ok = ptx::mbar_wait(bar(V_FULL + st), ph, s_abort);
+        SKB_TR(0, j, 0);
         for (int t = 0; t < 2 && ok; ++t) {
           if (j < ntile[t]) {
             ok = ptx::mbar_wait(bar(P_FULL + t), (uint32_t)j & 1u, s_abort);
             if (!ok) break;
+            SKB_TR(0, j, 1 + 3 * t);
             ptx::tc_fence_after();
             issue_pv(t, st, j);
+            SKB_TR(0, j, 2 + 3 * t);
             if (j == ntile[t] - 1) ptx::mma_commit(bar(O_DONE + t));
           }
           if (t == 1) ptx::mma_commit(bar(V_EMPTY + st));
@@ -200,6 +216,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             ptx::tc_fence_after();
             issue_qk(t, stn);
             ptx::mma_commit(bar(S_FULL + t));
+            SKB_TR(0, j, 3 + 3 * t);
           }
           if (t == 1 && j + 1 < nmax) ptx::mma_commit(bar(K_EMPTY + stn));
         }
@@ -228,11 +245,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ok = ptx::mbar_wait(bar(S_FULL + t), (uint32_t)j & 1u, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (wq == 0 && lane == 0) SKB_TR(1 + t, j, 0);
       ptx::tc_fence_after();
       uint32_t sr[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) ptx::tmem_ld32(tS + c * 32, sr + c * 32);
       ptx::tmem_wait_ld();
+      if (wq == 0 && lane == 0) SKB_TR(1 + t, j, 1);
 
       const int c0 = j * kTileN;
       if (__any_sync(0xffffffffu, c0 + kTileN - 1 > lim_col)) {
@@ -242,11 +261,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 128; c += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(sr[c]));
-        mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
+      for (int c = 0; c < 128; c += 8) {
+        mx0 = ptx::max3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+        mx1 = ptx::max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+        mx2 = ptx::max3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
+        mx3 = ptx::max3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
       const bool grow_m = mx > m + 8.f;   // false when both are -inf
@@ -257,16 +276,33 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         l *= alpha;
       }
       const float mref = (m == -INFINITY) ? 0.f : m;
-      float sum0 = 0.f, sum1 = 0.f;
+      if (wq == 0 && lane == 0) SKB_TR(1 + t, j, 2);
+      // Exponentials: of every four, two go to the MUFU unit and two to the FMA pipe (exp2_poly2),
+      // with the scale/subtract and the row sums done two lanes at a time.
+      const uint64_t sc2 = ptx::f2_pack(scale_log2, scale_log2), nm2 = ptx::f2_pack(-mref, -mref);
+      uint64_t sumA = ptx::f2_pack(0.f, 0.f), sumB = sumA;
 #pragma unroll
-      for (int c = 0; c < 128; c += 2) {
-        const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[c]), scale_log2, -mref));
-        const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[c + 1]), scale_log2, -mref));
-        sum0 += p0;
-        sum1 += p1;
+      for (int c = 0; c < 128; c += 4) {
+        const uint64_t xa = ptx::f2_fma(ptx::f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nm2);
+        const uint64_t xb = ptx::f2_fma(ptx::f2_pack(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2, nm2);
+        float x0, x1, x2, x3, p0, p1, p2, p3;
+        ptx::f2_unpack(xa, x0, x1);
+        ptx::f2_unpack(xb, x2, x3);
+        p0 = ptx::ex2(x0);
+        p1 = ptx::ex2(x1);
+        ptx::exp2_poly2(x2, x3, p2, p3);
+        sumA = ptx::f2_add(sumA, ptx::f2_pack(p0, p1));
+        sumB = ptx::f2_add(sumB, ptx::f2_pack(p2, p3));
         sr[c >> 1] = pack2(p0, p1, T());
+        sr[(c >> 1) + 1] = pack2(p2, p3, T());
       }
-      l += sum0 + sum1;
+      {
+        float a0, a1, b0, b1;
+        ptx::f2_unpack(sumA, a0, a1);
+        ptx::f2_unpack(sumB, b0, b1);
+        l += (a0 + a1) + (b0 + b1);
+      }
+      if (wq == 0 && lane == 0) SKB_TR(1 + t, j, 3);
       ptx::tmem_st32(tS, sr);
       ptx::tmem_st32(tS + 32, sr + 32);
       // S_t of tile j is only produced after PV_t of tile j-1 completed (same in-order issuer),
@@ -285,6 +321,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ptx::tmem_wait_st();
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(P_FULL + t));
+      if (wq == 0 && lane == 0) SKB_TR(1 + t, j, 4);
     }
 
     // ------------------------------------------------------------------ epilogue
@@ -294,7 +331,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     }
     if (ok) {
       ptx::tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool seen = (m != -INFINITY) && l > 0.f;    // false: no visible key in the whole row
+      const float inv = seen ? 1.f / l : 0.f;
       T* orow = o + ((size_t)bhq * Sq + (size_t)min(grow, Sq - 1)) * HD;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
@@ -318,7 +356,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
       }
-      if (grow < Sq) lse[(size_t)bhq * Sq + grow] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
+      if (grow < Sq) lse[(size_t)bhq * Sq + grow] = seen ? (m + log2f(l)) * kLn2 : -INFINITY;
     } else if (lane == 0) {
       atomicCAS(&g_dev_status, 0u, (3u << 16) | (unsigned)warp);
     }

@@ -486,6 +486,14 @@ int skb_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, 
   }
 }
 
+#ifdef SKB_TRACE
+/* Development only: copies the forward kernel's timeline trace to the host. */
+int skb_trace_read(long long* out, int n) {
+  SKB_CUDA(cudaMemcpyFromSymbol(out, skb::sm100::g_trace, sizeof(long long) * n));
+  return SKB_OK;
+}
+#endif
+
 /* Reads and clears the device status word written by bounded waits that gave up
  * (0 = no kernel of this library has timed out on the current device).  Synchronises the device. */
 int skb_device_status(unsigned int* status_out) {

@@ -161,6 +161,54 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// ---------------------------------------------------------------- packed fp32 math (two lanes per instruction)
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// 2^x for a pair of values on the FMA pipe instead of the MUFU unit (which tops out at 16
+// exponentials per clock per SM and would otherwise bound the softmax): round x to the nearest
+// integer n with the 1.5*2^23 trick, evaluate a degree-3 minimax polynomial of 2^f on
+// f = x - n in [-0.5, 0.5] (max relative error 7.5e-5, far below 16-bit rounding of P), then add n
+// to the exponent field.  Inputs are clamped to >= -126, so -inf gives ~1e-38 rather than 0.
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  const uint64_t x = f2_pack(x0, x1);
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f);
+  const uint64_t t = f2_add(x, magic);
+  const uint64_t xr = f2_add(t, f2_pack(-12582912.f, -12582912.f));
+  const uint64_t f = f2_fma(xr, f2_pack(-1.f, -1.f), x);
+  uint64_t q = f2_fma(f2_pack(0.0551716685f, 0.0551716685f), f, f2_pack(0.2426111251f, 0.2426111251f));
+  q = f2_fma(q, f, f2_pack(0.6932609677f, 0.6932609677f));
+  q = f2_fma(q, f, f2_pack(0.9999280572f, 0.9999280572f));
+  float q0, q1, t0, t1;
+  f2_unpack(q, q0, q1);
+  f2_unpack(t, t0, t1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 template <int N> __device__ __forceinline__ void setmaxnreg_inc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
