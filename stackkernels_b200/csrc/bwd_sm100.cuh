@@ -8,64 +8,80 @@
 // (flash_bwd.py:58-198, 7 tile GEMMs per tile pair), dQ is produced here from the same dS with
 // 5 GEMMs per pair and added into an fp32 accumulator in global memory.
 //
-// Everything is computed transposed so that probabilities can feed the next MMA from TMEM:
-//   (a) S^T  = K Q^T          [kv x q]   A = K (smem), B = Q (smem)            -> TMEM R_S
-//   (b) dP^T = V dO^T         [kv x q]   A = V (smem), B = dO (smem)           -> TMEM R_P
-//       P^T  = exp2(S^T * scale*log2e - LSE*log2e)          (16-bit, stored over R_S)
-//   (c) dV  += P^T dO         [kv x d]   A = P^T (TMEM), B = dO (smem, MN-major)
-//       dS^T = P^T o (dP^T - Delta)                         (16-bit, to shared memory)
-//   (d) dK  += dS^T Q         [kv x d]   A = dS^T (smem), B = Q (smem, MN-major)
-//   (e) dQ^T = K^T dS^T       [d x q]    A = K (smem, MN-major), B = dS^T (smem, MN-major) -> R_P
-// TMEM columns: dK [0,128) dV [128,256) R_S [256,384) R_P [384,512).
+// Everything is computed transposed so that probabilities can feed the next MMA from TMEM.  A work unit
+// is (query head, 64 query rows); per unit, with 128 KV rows as the M dimension:
+//   (a) S^T  = K Q^T      [kv128 x q64]  A = K (smem), B = Q (smem)               -> TMEM S[w]
+//   (b) dP^T = V dO^T     [kv128 x q64]  A = V (smem), B = dO (smem)              -> TMEM R[w]
+//       P^T  = exp2(S^T * scale*log2e - LSE*log2e)        (16-bit, stored over the start of S[w])
+//   (c) dV  += P^T dO     [kv128 x d128] A = P^T (TMEM), B = dO (smem, MN-major)
+//       dS^T = P^T o (dP^T - Delta)                       (16-bit, to shared memory dS[w])
+//   (d) dK  += dS^T Q     [kv128 x d128] A = dS^T (smem), B = Q (smem, MN-major)
+//   (e) dQ^T = K^T dS^T   [d128 x q64]   A = K (smem, MN-major), B = dS^T (smem, MN-major) -> TMEM R[w]
+// TMEM columns: dK [0,128) dV [128,256) S[0] S[1] [256,384) R[0] R[1] [384,512): the score and dP/dQ
+// buffers are double buffered, one pair per compute warpgroup, so consecutive units overlap freely.
 //
-// Warps: 0 TMA producer, 1 MMA issuer, 2 TMEM owner, 4-11 two compute warpgroups that split the
-// 128 query columns of every tile (thread = one KV row = one TMEM lane, 64 columns).
-// The issue order c(i) b(i) a(i+1) d(i) e(i) lets the tensor core run dV / the next S^T while the
-// compute warps turn dP^T into dS^T, and d/e while they compute the next P^T and drain dQ^T.
+// Warps: 0 TMA producer (K, V once; Q and dO through 3-stage rings), 1 MMA issuer, 2 TMEM owner,
+// 4-7 compute warpgroup 0 (even units), 8-11 compute warpgroup 1 (odd units); a compute thread owns
+// one TMEM lane (a KV row of S^T / dP^T, a d index of dQ^T) and all 64 columns of its unit.
+// Per unit u the issuer queues  a(u+1)  c(u)  b(u+1)  d(u)  e(u):  while one warpgroup turns scores
+// into P^T / dS^T or drains dQ^T, the tensor core works on the other warpgroup's unit.
+// dQ^T is drained straight from registers with coalesced fp32 reductions (128 B per warp instruction).
 #pragma once
-#include "sm100_ptx.cuh"
+#include "fwd_sm100.cuh"   // Fmt<>, pack2()
 
 namespace skb {
 namespace sm100 {
 
 constexpr int kBwdThreads = 384;
 constexpr int kBwdTile = 128;
-constexpr int kBwdBox = 128 * 128;                 // 128 rows x 64 16-bit columns
-constexpr int kBwdTileBytes = 2 * kBwdBox;         // 128 x 128 16-bit tile
-constexpr int kBwdQStage = kBwdTileBytes + 1024;   // Q tile + LSE*log2e row (512 B) + Delta row (512 B)
+constexpr int kBwdQ = 64;                          // query rows per work unit
+constexpr int kBwdBox = 128 * 128;                 // K/V box: 128 rows x 64 16-bit columns
+constexpr int kBwdTileBytes = 2 * kBwdBox;         // 128 x 128 16-bit tile (K, V)
+constexpr int kBwdQBox = kBwdQ * 128;              // Q/dO box: 64 rows x 64 16-bit columns
+constexpr int kBwdQTile = 2 * kBwdQBox;            // 64 x 128 16-bit tile (Q, dO); also one dS^T tile (128 x 64)
+constexpr int kBwdStages = 3;
 
 enum BwdBar {
   B_KV_FULL = 0,
-  B_Q_FULL = 1,     // +stage
-  B_Q_EMPTY = 3,    // +stage
-  B_DO_FULL = 5,    // +stage
-  B_DO_EMPTY = 7,   // +stage
-  B_S_READY = 9,    // MMA -> compute
-  B_P_READY = 10,   // compute -> MMA (256)
-  B_DP_READY = 11,  // MMA -> compute
-  B_DS_READY = 12,  // compute -> MMA (256)
-  B_DQ_DONE = 13,   // MMA -> compute
-  B_RP_FREE = 14,   // compute -> MMA (256)
-  B_ACC_DONE = 15,
-  B_NUM = 16
+  B_Q_FULL = 1,      // +stage (3)
+  B_Q_EMPTY = 4,     // +stage
+  B_DO_FULL = 7,     // +stage
+  B_DO_EMPTY = 10,   // +stage
+  B_S_READY = 13,    // +w  MMA -> compute warpgroup w
+  B_P_READY = 15,    // +w  compute -> MMA (128)
+  B_DP_READY = 17,   // +w  MMA -> compute
+  B_DS_READY = 19,   // +w  compute -> MMA (128)
+  B_DQ_DONE = 21,    // +w  MMA -> compute
+  B_RP_FREE = 23,    // +w  compute -> MMA (128)
+  B_ACC_DONE = 25,
+  B_NUM = 26
 };
 
-// shared memory: K, V, dS tiles, 2 Q stages, 2 dO stages, barriers
-constexpr int kBwdSmemUsed = 3 * kBwdTileBytes + 2 * kBwdQStage + 2 * kBwdTileBytes + 256;
-constexpr int kBwdSmemBytes = 232448;   // everything the SM offers one CTA; leaves alignment slack
+// shared memory: K, V tiles; 3 Q stages; 3 dO stages; 2 dS^T tiles; per-stage -LSE*log2e / -Delta rows; barriers
+constexpr int kBwdSmemUsed = 2 * kBwdTileBytes + (2 * kBwdStages + 2) * kBwdQTile + kBwdStages * 512 + 256;
+constexpr int kBwdSmemBytes = kBwdSmemUsed + 1024;
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ void red_add(float* addr, float v) {
+#ifdef SKB_PROBE_NO_RED   // development probe: how much of the kernel time is the dQ reduction traffic
+  return;
+#endif
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
 
-// Preprocess: delta = rowsum(dO o O) and lse2 = LSE*log2e, both padded to a multiple of 128 rows per
-// (batch, head) so that the main kernel can fetch 128-row slices with aligned bulk copies.
-// Padding rows and rows without any visible key get lse2 = +inf (their probabilities become 0).
+// Preprocess: delta = -rowsum(dO o O) and lse2 = -LSE*log2e (both NEGATED, so the main kernel only adds),
+// padded to a multiple of 128 rows per (batch, head) so that the main kernel can fetch 64-row slices with
+// aligned bulk copies.  Padding rows and rows without any visible key get lse2 = -inf, which makes their
+// probabilities (numerically) zero.
 template <typename T>
 __global__ void __launch_bounds__(256)
 bwd_prep_kernel(const T* __restrict__ dout, const T* __restrict__ o, const float* __restrict__ lse,
@@ -77,7 +93,7 @@ bwd_prep_kernel(const T* __restrict__ dout, const T* __restrict__ o, const float
   const size_t bh = prow / Sq_pad;
   const int r = (int)(prow % Sq_pad);
   if (r >= Sq) {
-    if (lane == 0) { delta[prow] = 0.f; lse2[prow] = INFINITY; }
+    if (lane == 0) { delta[prow] = 0.f; lse2[prow] = -INFINITY; }
     return;
   }
   const size_t row = bh * Sq + r;
@@ -92,9 +108,9 @@ bwd_prep_kernel(const T* __restrict__ dout, const T* __restrict__ o, const float
 #pragma unroll
   for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
   if (lane == 0) {
-    delta[prow] = s;
+    delta[prow] = -s;
     const float l = lse[row];
-    lse2[prow] = (l == -INFINITY) ? INFINITY : l * kLog2e;
+    lse2[prow] = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
   }
 }
 
@@ -109,6 +125,7 @@ bwd_post_kernel(const float* __restrict__ acc, T* __restrict__ dq, float scale, 
   *reinterpret_cast<uint2*>(dq + i * 4) = *reinterpret_cast<uint2*>(out);
 }
 
+
 template <typename T>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -117,9 +134,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
            T* __restrict__ dk, T* __restrict__ dv, int Hq, int Hkv, int Sq, int Sk, int Sq_pad, int causal,
            float scale, float scale_log2) {
   constexpr int HD = 128;
-  constexpr uint32_t IDESC_KK = ptx::idesc_f16(Fmt<T>::v, 128, 128, 0, 0);   // A K-major,  B K-major
-  constexpr uint32_t IDESC_KM = ptx::idesc_f16(Fmt<T>::v, 128, 128, 0, 1);   // A K-major,  B MN-major
-  constexpr uint32_t IDESC_MM = ptx::idesc_f16(Fmt<T>::v, 128, 128, 1, 1);   // A MN-major, B MN-major
+  constexpr uint32_t IDESC_S = ptx::idesc_f16(Fmt<T>::v, 128, kBwdQ, 0, 0);    // (a),(b): A K-major, B K-major, N = 64
+  constexpr uint32_t IDESC_KM = ptx::idesc_f16(Fmt<T>::v, 128, 128, 0, 1);     // (c),(d): A K-major, B MN-major
+  constexpr uint32_t IDESC_DQ = ptx::idesc_f16(Fmt<T>::v, 128, kBwdQ, 1, 1);   // (e): A MN-major, B MN-major, N = 64
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -127,15 +144,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   uint8_t* gbase = smem_raw + (sbase - raw);
   const uint32_t sK = sbase;
   const uint32_t sV = sK + kBwdTileBytes;
-  const uint32_t sdS = sV + kBwdTileBytes;
-  const uint32_t sQ0 = sdS + kBwdTileBytes;                 // 2 stages of kBwdQStage
-  const uint32_t sdO0 = sQ0 + 2 * kBwdQStage;               // 2 stages of kBwdTileBytes
-  const uint32_t sBar = sdO0 + 2 * kBwdTileBytes;
+  const uint32_t sQ0 = sV + kBwdTileBytes;                       // kBwdStages tiles of kBwdQTile
+  const uint32_t sdO0 = sQ0 + kBwdStages * kBwdQTile;            // kBwdStages tiles
+  const uint32_t sdS0 = sdO0 + kBwdStages * kBwdQTile;           // 2 tiles (128 kv rows x 64 q)
+  const uint32_t sStat0 = sdS0 + 2 * kBwdQTile;                  // kBwdStages x (64 floats -lse2, 64 floats -delta)
+  const uint32_t sBar = sStat0 + kBwdStages * 512;
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gbase + (sBar - sbase) + B_NUM * 8);
   volatile int* s_abort = reinterpret_cast<volatile int*>(gbase + (sBar - sbase) + B_NUM * 8 + 8);
   auto bar = [&](int i) -> uint32_t { return sBar + 8u * (uint32_t)i; };
-  auto sQ = [&](int st) -> uint32_t { return sQ0 + (uint32_t)st * kBwdQStage; };
-  auto sdO = [&](int st) -> uint32_t { return sdO0 + (uint32_t)st * kBwdTileBytes; };
+  auto sQ = [&](int st) -> uint32_t { return sQ0 + (uint32_t)st * kBwdQTile; };
+  auto sdO = [&](int st) -> uint32_t { return sdO0 + (uint32_t)st * kBwdQTile; };
+  auto sdS = [&](int w) -> uint32_t { return sdS0 + (uint32_t)w * kBwdQTile; };
 
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
@@ -143,19 +162,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int G = Hq / Hkv;
   const int shift = Sk - Sq;
   const int kv0 = jt * kBwdTile;
-  const int nq = cdiv(Sq, kBwdTile);
-  int i_start = 0;
-  if (causal) i_start = max(0, kv0 - shift) / kBwdTile;      // first query tile that sees key kv0
-  const int per_head = max(0, nq - i_start);
-  const int n_it = per_head * G;
-  const bool fits = (sbase - raw) + (uint32_t)kBwdSmemUsed <= (uint32_t)kBwdSmemBytes;
+  const int nq = cdiv(Sq, kBwdQ);                                 // 64-row query chunks per head
+  int s_start = 0;
+  if (causal) s_start = max(0, kv0 - shift) / kBwdQ;              // first chunk that sees key kv0
+  const int per_head = max(0, nq - s_start);
+  const int n_run = per_head * G;                                  // work units of this CTA
 
   if (threadIdx.x == 0) {
-    *s_abort = fits ? 0 : 1;
-    for (int i = 0; i < B_NUM; ++i)
-      ptx::mbar_init(bar(i), (i == B_P_READY || i == B_DS_READY || i == B_RP_FREE) ? 256u : 1u);
+    *s_abort = 0;
+    for (int i = 0; i < B_NUM; ++i) {
+      const bool from_wg = (i >= B_P_READY && i < B_P_READY + 2) || (i >= B_DS_READY && i < B_DS_READY + 2) ||
+                           (i >= B_RP_FREE && i < B_RP_FREE + 2);
+      ptx::mbar_init(bar(i), from_wg ? 128u : 1u);
+    }
     ptx::fence_mbar_init();
-    if (!fits) atomicCAS(&g_dev_status, 0u, (6u << 16));
   }
   if (warp == 2) {
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(s_tmem)), 512);
@@ -165,12 +185,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const uint32_t tDK = tmem, tDV = tmem + 128, tRS = tmem + 256, tRP = tmem + 384;
-  const int n_run = fits ? n_it : 0;
+  const uint32_t tDK = tmem, tDV = tmem + 128;
+  auto tS = [&](int w) -> uint32_t { return tmem + 256 + 64 * (uint32_t)w; };
+  auto tR = [&](int w) -> uint32_t { return tmem + 384 + 64 * (uint32_t)w; };
 
-  // iteration -> (query head, query tile)
-  auto head_of = [&](int it) { return hkv * G + it / per_head; };
-  auto tile_of = [&](int it) { return i_start + it % per_head; };
+  // unit -> (query head, first query row)
+  auto head_of = [&](int u) { return hkv * G + u / per_head; };
+  auto row_of = [&](int u) { return (s_start + u % per_head) * kBwdQ; };
 
   if (warp < 4) {
     ptx::setmaxnreg_dec<56>();
@@ -183,83 +204,88 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         ptx::tma_load_3d(sV + h * kBwdBox, &tm_v, h * 64, kv0, b * Hkv + hkv, bar(B_KV_FULL));
       }
       bool ok = true;
-      for (int it = 0; it < n_run && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (uint32_t)((it >> 1) & 1) ^ 1u;
-        const int bh = b * Hq + head_of(it), q0 = tile_of(it) * kBwdTile;
+      for (int u = 0; u < n_run && ok; ++u) {
+        const int st = u % kBwdStages;
+        const uint32_t ph = (uint32_t)((u / kBwdStages) & 1) ^ 1u;
+        const int bh = b * Hq + head_of(u), q0 = row_of(u);
         ok = ptx::mbar_wait(bar(B_Q_EMPTY + st), ph, s_abort);
         if (!ok) break;
-        ptx::mbar_expect_tx(bar(B_Q_FULL + st), kBwdQStage);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sQ(st) + h * kBwdBox, &tm_q, h * 64, q0, bh, bar(B_Q_FULL + st));
-        bulk_load_1d(sQ(st) + kBwdTileBytes, lse2 + (size_t)bh * Sq_pad + q0, 512, bar(B_Q_FULL + st));
-        bulk_load_1d(sQ(st) + kBwdTileBytes + 512, delta + (size_t)bh * Sq_pad + q0, 512, bar(B_Q_FULL + st));
+        ptx::mbar_expect_tx(bar(B_Q_FULL + st), kBwdQTile + 512);
+        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sQ(st) + h * kBwdQBox, &tm_q, h * 64, q0, bh, bar(B_Q_FULL + st));
+        bulk_load_1d(sStat0 + st * 512, lse2 + (size_t)bh * Sq_pad + q0, 256, bar(B_Q_FULL + st));
+        bulk_load_1d(sStat0 + st * 512 + 256, delta + (size_t)bh * Sq_pad + q0, 256, bar(B_Q_FULL + st));
         ok = ptx::mbar_wait(bar(B_DO_EMPTY + st), ph, s_abort);
         if (!ok) break;
-        ptx::mbar_expect_tx(bar(B_DO_FULL + st), kBwdTileBytes);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sdO(st) + h * kBwdBox, &tm_do, h * 64, q0, bh, bar(B_DO_FULL + st));
+        ptx::mbar_expect_tx(bar(B_DO_FULL + st), kBwdQTile);
+        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sdO(st) + h * kBwdQBox, &tm_do, h * 64, q0, bh, bar(B_DO_FULL + st));
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (7u << 16));
     } else if (warp == 1 && lane == 0 && n_run > 0) {
       // ------------------------------------------------------------------ MMA issuer
       bool ok = true;
-      // k-step offsets: K-major operands step 32 bytes inside a 128-byte row and switch box after 4 steps;
-      // MN-major operands step 16 rows (2048 bytes).
-      auto koff = [](int kk) -> uint32_t { return (uint32_t)(kk >> 2) * kBwdBox + (uint32_t)(kk & 3) * 32u; };
-      auto issue_a = [&](int st) {   // S^T = K Q^T
+      // K-major operands advance 32 bytes per k-step inside a 128-byte row and change box after 4 steps;
+      // MN-major operands advance 16 rows (2048 bytes) per k-step.
+      auto issue_a = [&](int u) {   // S^T = K Q^T -> S[u & 1]
+        const uint32_t q = sQ(u % kBwdStages);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          ptx::mma_ss(tRS, ptx::desc_sw128_kmajor(sK + koff(kk)), ptx::desc_sw128_kmajor(sQ(st) + koff(kk)), IDESC_KK, kk > 0);
+          ptx::mma_ss(tS(u & 1), ptx::desc_sw128_kmajor(sK + (kk >> 2) * kBwdBox + (kk & 3) * 32),
+                      ptx::desc_sw128_kmajor(q + (kk >> 2) * kBwdQBox + (kk & 3) * 32), IDESC_S, kk > 0);
+        ptx::mma_commit(bar(B_S_READY + (u & 1)));
       };
+      auto issue_b = [&](int u) {   // dP^T = V dO^T -> R[u & 1]
+        const uint32_t d = sdO(u % kBwdStages);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          ptx::mma_ss(tR(u & 1), ptx::desc_sw128_kmajor(sV + (kk >> 2) * kBwdBox + (kk & 3) * 32),
+                      ptx::desc_sw128_kmajor(d + (kk >> 2) * kBwdQBox + (kk & 3) * 32), IDESC_S, kk > 0);
+        ptx::mma_commit(bar(B_DP_READY + (u & 1)));
+      };
+      auto stage_parity = [](int u) -> uint32_t { return (uint32_t)(u / kBwdStages) & 1u; };
       ok = ptx::mbar_wait(bar(B_KV_FULL), 0, s_abort) && ptx::mbar_wait(bar(B_Q_FULL), 0, s_abort);
-      if (ok) {
-        ptx::tc_fence_after();
-        issue_a(0);
-        ptx::mma_commit(bar(B_S_READY));
-      }
-      for (int it = 0; it < n_run && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (uint32_t)it & 1u;
-        ok = ptx::mbar_wait(bar(B_DO_FULL + st), (uint32_t)(it >> 1) & 1u, s_abort) &&
-             ptx::mbar_wait(bar(B_P_READY), ph, s_abort);
-        if (!ok) break;
-        ptx::tc_fence_after();
-        // (c) dV += P^T dO : P^T columns of query half h sit at R_S + 64h + [0,32)
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          ptx::mma_ts(tDV, tRS + (kk >> 2) * 64 + (kk & 3) * 8, ptx::desc_sw128_mnmajor(sdO(st) + kk * 2048, kBwdBox),
-                      IDESC_KM, (it > 0) || (kk > 0));
-        if (it > 0) {
-          ok = ptx::mbar_wait(bar(B_RP_FREE), (uint32_t)(it - 1) & 1u, s_abort);
+      if (ok) { ptx::tc_fence_after(); issue_a(0); }
+      if (ok) ok = ptx::mbar_wait(bar(B_DO_FULL), 0, s_abort);
+      if (ok) { ptx::tc_fence_after(); issue_b(0); }
+      for (int u = 0; u < n_run && ok; ++u) {
+        const int w = u & 1, st = u % kBwdStages;
+        const uint32_t ph = (uint32_t)(u >> 1) & 1u;       // per-warpgroup barriers complete once per own unit
+        if (u + 1 < n_run) {
+          ok = ptx::mbar_wait(bar(B_Q_FULL + (u + 1) % kBwdStages), stage_parity(u + 1), s_abort);
           if (!ok) break;
           ptx::tc_fence_after();
+          issue_a(u + 1);
         }
-        // (b) dP^T = V dO^T
+        ok = ptx::mbar_wait(bar(B_P_READY + w), ph, s_abort);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        // (c) dV += P^T dO : A = P^T in TMEM (4 k-steps of 16 query rows), B = dO MN-major
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          ptx::mma_ss(tRP, ptx::desc_sw128_kmajor(sV + koff(kk)), ptx::desc_sw128_kmajor(sdO(st) + koff(kk)), IDESC_KK, kk > 0);
-        ptx::mma_commit(bar(B_DP_READY));
+        for (int kk = 0; kk < 4; ++kk)
+          ptx::mma_ts(tDV, tS(w) + kk * 8, ptx::desc_sw128_mnmajor(sdO(st) + kk * 2048, kBwdQBox), IDESC_KM,
+                      (u > 0) || (kk > 0));
         ptx::mma_commit(bar(B_DO_EMPTY + st));
-        if (it + 1 < n_run) {
-          ok = ptx::mbar_wait(bar(B_Q_FULL + (st ^ 1)), (uint32_t)((it + 1) >> 1) & 1u, s_abort);
+        if (u + 1 < n_run) {
+          ok = ptx::mbar_wait(bar(B_DO_FULL + (u + 1) % kBwdStages), stage_parity(u + 1), s_abort);
+          // R[w^1] still holds dQ^T of unit u-1 until that warpgroup has pulled it into registers
+          if (ok && u >= 1) ok = ptx::mbar_wait(bar(B_RP_FREE + (w ^ 1)), (uint32_t)((u - 1) >> 1) & 1u, s_abort);
           if (!ok) break;
           ptx::tc_fence_after();
-          issue_a(st ^ 1);
-          ptx::mma_commit(bar(B_S_READY));
+          issue_b(u + 1);
         }
-        ok = ptx::mbar_wait(bar(B_DS_READY), ph, s_abort);
+        ok = ptx::mbar_wait(bar(B_DS_READY + w), ph, s_abort);
         if (!ok) break;
         ptx::tc_fence_after();
-        // (d) dK += dS^T Q
+        // (d) dK += dS^T Q : A = dS^T (smem, K-major, 4 k-steps), B = Q MN-major
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          ptx::mma_ss(tDK, ptx::desc_sw128_kmajor(sdS(w) + kk * 32), ptx::desc_sw128_mnmajor(sQ(st) + kk * 2048, kBwdQBox),
+                      IDESC_KM, (u > 0) || (kk > 0));
+        // (e) dQ^T = K^T dS^T -> R[w] : A = K MN-major (8 k-steps over KV rows), B = dS^T MN-major
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          ptx::mma_ss(tDK, ptx::desc_sw128_kmajor(sdS + koff(kk)), ptx::desc_sw128_mnmajor(sQ(st) + kk * 2048, kBwdBox),
-                      IDESC_KM, (it > 0) || (kk > 0));
-        // (e) dQ^T = K^T dS^T
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          ptx::mma_ss(tRP, ptx::desc_sw128_mnmajor(sK + kk * 2048, kBwdBox), ptx::desc_sw128_mnmajor(sdS + kk * 2048, kBwdBox),
-                      IDESC_MM, kk > 0);
-        ptx::mma_commit(bar(B_DQ_DONE));
+          ptx::mma_ss(tR(w), ptx::desc_sw128_mnmajor(sK + kk * 2048, kBwdBox), ptx::desc_sw128_mnmajor(sdS(w) + kk * 2048, kBwdQTile),
+                      IDESC_DQ, kk > 0);
+        ptx::mma_commit(bar(B_DQ_DONE + w));
         ptx::mma_commit(bar(B_Q_EMPTY + st));
       }
       ptx::mma_commit(bar(B_ACC_DONE));
@@ -269,115 +295,121 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   } else {
     ptx::setmaxnreg_inc<224>();
     // -------------------------------------------------------------------- compute warpgroups
-    const int h = (warp - 4) >> 2;                 // which 64 query columns of the tile
+    const int w = (warp - 4) >> 2;                 // warpgroup: handles units u with (u & 1) == w
     const int wq = warp & 3;
     const int r = wq * 32 + lane;                  // TMEM lane: KV row in S^T / dP^T, d index in dQ^T
     const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
     const int kvidx = kv0 + r;
-    float p[64];
+    const uint64_t sc2 = ptx::f2_pack(scale_log2, scale_log2);
     bool ok = true;
 
-    // P^T for iteration `it`: exp2(S^T*scale*log2e - lse2[q]), masked, kept in p[] and stored to TMEM
-    auto compute_p = [&](int it) -> bool {
-      const int st = it & 1;
-      bool w = ptx::mbar_wait(bar(B_Q_FULL + st), (uint32_t)(it >> 1) & 1u, s_abort) &&
-               ptx::mbar_wait(bar(B_S_READY), (uint32_t)it & 1u, s_abort);
-      w = __all_sync(0xffffffffu, w);
-      if (!w) return false;
+    for (int u = w; u < n_run; u += 2) {
+      const int st = u % kBwdStages;
+      const uint32_t ph = (uint32_t)(u >> 1) & 1u;
+      const int q0 = row_of(u);
+      const float* stat = reinterpret_cast<const float*>(gbase + (sStat0 - sbase) + st * 512);   // -lse2[64], -delta[64]
+      // ---- P^T = exp2(S^T*scale*log2e - LSE*log2e), masked; half of the exponentials on the FMA pipe
+      ok = ptx::mbar_wait(bar(B_Q_FULL + st), (uint32_t)(u / kBwdStages) & 1u, s_abort) &&
+           ptx::mbar_wait(bar(B_S_READY + w), ph, s_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       ptx::tc_fence_after();
-      const float* l2 = reinterpret_cast<const float*>(gbase + (sQ(st) - sbase) + kBwdTileBytes) + 64 * h;
-      const int q0 = tile_of(it) * kBwdTile + 64 * h;
       // visible iff kvidx <= q + shift  <=>  column c >= kvidx - shift - q0
       const int cmin = causal ? kvidx - shift - q0 : -1;
-      uint32_t pk[32];
+      uint64_t p2[32];                             // the unit's 64 probabilities of this KV row, as fp32 pairs
+      {
+        uint32_t pk[32];
 #pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {
-        uint32_t sr[32];
-        ptx::tmem_ld32(tRS + t_lane + 64 * h + 32 * c2, sr);
-        ptx::tmem_wait_ld();
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t sr[32];
+          ptx::tmem_ld32(tS(w) + t_lane + 32 * c2, sr);
+          ptx::tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; c += 4) {
-          const float4 lv = *reinterpret_cast<const float4*>(l2 + 32 * c2 + c);
-          const float le[4] = {lv.x, lv.y, lv.z, lv.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int cc = 32 * c2 + c + e;
-            float v = ptx::ex2(fmaf(__uint_as_float(sr[c + e]), scale_log2, -le[e]));
-            if (cc < cmin) v = 0.f;
-            p[cc] = v;
+          for (int c = 0; c < 32; c += 4) {
+            const int cc = 32 * c2 + c;
+            const float4 lv = *reinterpret_cast<const float4*>(stat + cc);
+            const uint64_t xa = ptx::f2_fma(ptx::f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2,
+                                            ptx::f2_pack(lv.x, lv.y));
+            const uint64_t xb = ptx::f2_fma(ptx::f2_pack(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2,
+                                            ptx::f2_pack(lv.z, lv.w));
+            float x0, x1, x2, x3, v0, v1, v2, v3;
+            ptx::f2_unpack(xa, x0, x1);
+            ptx::f2_unpack(xb, x2, x3);
+            v0 = ptx::ex2(x0);
+            v1 = ptx::ex2(x1);
+            ptx::exp2_poly2(x2, x3, v2, v3);
+            if (cc < cmin) v0 = 0.f;
+            if (cc + 1 < cmin) v1 = 0.f;
+            if (cc + 2 < cmin) v2 = 0.f;
+            if (cc + 3 < cmin) v3 = 0.f;
+            p2[cc >> 1] = ptx::f2_pack(v0, v1);
+            p2[(cc >> 1) + 1] = ptx::f2_pack(v2, v3);
+            pk[cc >> 1] = pack2(v0, v1, T());
+            pk[(cc >> 1) + 1] = pack2(v2, v3, T());
           }
         }
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) pk[16 * c2 + (c >> 1)] = pack2(p[32 * c2 + c], p[32 * c2 + c + 1], T());
+        ptx::tmem_st32(tS(w) + t_lane, pk);
+        ptx::tmem_wait_st();
       }
-      ptx::tmem_st32(tRS + t_lane + 64 * h, pk);
-      ptx::tmem_wait_st();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(bar(B_P_READY));
-      return true;
-    };
+      ptx::mbar_arrive(bar(B_P_READY + w));
 
-    if (n_run > 0) ok = compute_p(0);
-    for (int it = 0; it < n_run && ok; ++it) {
-      const int st = it & 1;
-      const uint32_t ph = (uint32_t)it & 1u;
-      // ---- dS^T = P^T o (dP^T - Delta) -> shared memory (rows = KV, 64 query columns per 128-byte row)
-      ok = ptx::mbar_wait(bar(B_DP_READY), ph, s_abort);
+      // ---- dS^T = P^T o (dP^T - Delta) -> shared memory tile dS[w] (rows = KV, 64 query columns = 128 bytes)
+      ok = ptx::mbar_wait(bar(B_DP_READY + w), ph, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after();
       {
-        const float* dl = reinterpret_cast<const float*>(gbase + (sQ(st) - sbase) + kBwdTileBytes + 512) + 64 * h;
-        uint8_t* ds_row = gbase + (sdS - sbase) + h * kBwdBox + r * 128;
+        uint8_t* ds_row = gbase + (sdS(w) - sbase) + r * 128;
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2) {
           uint32_t dr[32];
-          ptx::tmem_ld32(tRP + t_lane + 64 * h + 32 * c2, dr);
+          ptx::tmem_ld32(tR(w) + t_lane + 32 * c2, dr);
           ptx::tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
-            const float4 d0 = *reinterpret_cast<const float4*>(dl + 32 * c2 + c);
-            const float4 d1 = *reinterpret_cast<const float4*>(dl + 32 * c2 + c + 4);
-            const float de[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-            float ds[8];
+            const int cc = 32 * c2 + c;
+            const float4 d0 = *reinterpret_cast<const float4*>(stat + 64 + cc);
+            const float4 d1 = *reinterpret_cast<const float4*>(stat + 64 + cc + 4);
+            const uint64_t nd[4] = {ptx::f2_pack(d0.x, d0.y), ptx::f2_pack(d0.z, d0.w), ptx::f2_pack(d1.x, d1.y),
+                                    ptx::f2_pack(d1.z, d1.w)};
+            uint32_t wv[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) ds[e] = p[32 * c2 + c + e] * (__uint_as_float(dr[c + e]) - de[e]);
-            uint4 w;
-            w.x = pack2(ds[0], ds[1], T()); w.y = pack2(ds[2], ds[3], T());
-            w.z = pack2(ds[4], ds[5], T()); w.w = pack2(ds[6], ds[7], T());
-            const int chunk = (32 * c2 + c) >> 3;
-            *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (r & 7)) << 4)) = w;
+            for (int e = 0; e < 4; ++e) {
+              const uint64_t dp = ptx::f2_pack(__uint_as_float(dr[c + 2 * e]), __uint_as_float(dr[c + 2 * e + 1]));
+              float a0, a1;
+              ptx::f2_unpack(f2_mul(p2[(cc >> 1) + e], ptx::f2_add(dp, nd[e])), a0, a1);
+              wv[e] = pack2(a0, a1, T());
+            }
+            *reinterpret_cast<uint4*>(ds_row + (((cc >> 3) ^ (r & 7)) << 4)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
           }
         }
       }
       fence_async_smem();          // make the generic-proxy stores visible to the tensor core
       ptx::tc_fence_before();
-      ptx::mbar_arrive(bar(B_DS_READY));
-      // ---- next tile's P^T while the tensor core runs dK and dQ^T of this one
-      if (it + 1 < n_run) {
-        ok = compute_p(it + 1);
-        if (!ok) break;
-      }
-      // ---- drain dQ^T (lane = d, columns = query rows) into the fp32 accumulator with coalesced reductions
-      ok = ptx::mbar_wait(bar(B_DQ_DONE), ph, s_abort);
+      ptx::mbar_arrive(bar(B_DS_READY + w));
+
+      // ---- drain dQ^T (lane = d, columns = query rows): pull it into registers, release the TMEM buffer,
+      //      then add into the fp32 accumulator; each warp instruction covers 128 contiguous bytes.
+      ok = ptx::mbar_wait(bar(B_DQ_DONE + w), ph, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after();
       {
-        const int q0 = tile_of(it) * kBwdTile + 64 * h;
-        float* dst = dq_acc + ((size_t)(b * Hq + head_of(it)) * Sq + q0) * HD + r;
+        uint32_t qa[32], qb[32];
+        ptx::tmem_ld32(tR(w) + t_lane, qa);
+        ptx::tmem_ld32(tR(w) + t_lane + 32, qb);
+        ptx::tmem_wait_ld();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar(B_RP_FREE + w));
+        float* dst = dq_acc + ((size_t)(b * Hq + head_of(u)) * Sq + q0) * HD + r;
 #pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2) {
-          uint32_t qr[32];
-          ptx::tmem_ld32(tRP + t_lane + 64 * h + 32 * c2, qr);
-          ptx::tmem_wait_ld();
+        for (int c = 0; c < 32; ++c)
+          if (q0 + c < Sq) red_add(dst + (size_t)c * HD, __uint_as_float(qa[c]));
 #pragma unroll
-          for (int c = 0; c < 32; ++c)
-            if (q0 + 32 * c2 + c < Sq) red_add(dst + (size_t)(32 * c2 + c) * HD, __uint_as_float(qr[c]));
-        }
+        for (int c = 0; c < 32; ++c)
+          if (q0 + 32 + c < Sq) red_add(dst + (size_t)(32 + c) * HD, __uint_as_float(qb[c]));
       }
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(bar(B_RP_FREE));
     }
 
     // ------------------------------------------------------------------ epilogue: dK, dV
@@ -385,18 +417,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ok = ptx::mbar_wait(bar(B_ACC_DONE), 0, s_abort);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok && fits) {
+    if (ok) {
       ptx::tc_fence_after();
       const size_t row = ((size_t)b * Hkv + hkv) * Sk + min(kvidx, Sk - 1);
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        T* dst = (which == 0 ? dk : dv) + row * HD + 64 * h;
+        T* dst = (which == 0 ? dk : dv) + row * HD + 64 * w;
         const float mul = which == 0 ? scale : 1.f;
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2) {
           uint32_t ar[32];
           if (n_run > 0) {
-            ptx::tmem_ld32((which == 0 ? tDK : tDV) + t_lane + 64 * h + 32 * c2, ar);
+            ptx::tmem_ld32((which == 0 ? tDK : tDV) + t_lane + 64 * w + 32 * c2, ar);
             ptx::tmem_wait_ld();
           } else {
 #pragma unroll
@@ -405,12 +437,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           if (kvidx < Sk) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
-              uint4 w;
-              w.x = pack2(__uint_as_float(ar[i]) * mul, __uint_as_float(ar[i + 1]) * mul, T());
-              w.y = pack2(__uint_as_float(ar[i + 2]) * mul, __uint_as_float(ar[i + 3]) * mul, T());
-              w.z = pack2(__uint_as_float(ar[i + 4]) * mul, __uint_as_float(ar[i + 5]) * mul, T());
-              w.w = pack2(__uint_as_float(ar[i + 6]) * mul, __uint_as_float(ar[i + 7]) * mul, T());
-              *reinterpret_cast<uint4*>(dst + 32 * c2 + i) = w;
+              uint4 o4;
+              o4.x = pack2(__uint_as_float(ar[i]) * mul, __uint_as_float(ar[i + 1]) * mul, T());
+              o4.y = pack2(__uint_as_float(ar[i + 2]) * mul, __uint_as_float(ar[i + 3]) * mul, T());
+              o4.z = pack2(__uint_as_float(ar[i + 4]) * mul, __uint_as_float(ar[i + 5]) * mul, T());
+              o4.w = pack2(__uint_as_float(ar[i + 6]) * mul, __uint_as_float(ar[i + 7]) * mul, T());
+              *reinterpret_cast<uint4*>(dst + 32 * c2 + i) = o4;
             }
           }
         }

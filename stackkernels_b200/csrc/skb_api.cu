@@ -7,7 +7,6 @@
 #include <cstring>
 
 #include "decode_group.cuh"
-#include "fwd_sm100.cuh"
 #include "bwd_sm100.cuh"
 #include "general_kernels.cuh"
 #include "skb200.h"
@@ -228,8 +227,8 @@ int launch_bwd_sm100(const void* dout, const void* q, const void* k, const void*
   const size_t bh = (size_t)B * Hq;
   CUtensorMap mq, mk, mv, mdo;
   const int dt = DtypeOf<T>::value;
-  if (int rc = make_map_3d(&mq, dt, q, D, Sq, bh)) return rc;
-  if (int rc = make_map_3d(&mdo, dt, dout, D, Sq, bh)) return rc;
+  if (int rc = make_map_3d(&mq, dt, q, D, Sq, bh, sm100::kBwdQ)) return rc;
+  if (int rc = make_map_3d(&mdo, dt, dout, D, Sq, bh, sm100::kBwdQ)) return rc;
   if (int rc = make_map_3d(&mk, dt, k, D, Sk, (size_t)B * Hkv)) return rc;
   if (int rc = make_map_3d(&mv, dt, v, D, Sk, (size_t)B * Hkv)) return rc;
 
