@@ -184,7 +184,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
-  const uint32_t tmem = *s_tmem;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, *s_tmem, 0);
   const uint32_t tDK = tmem, tDV = tmem + 128;
   auto tS = [&](int w) -> uint32_t { return tmem + 256 + 64 * (uint32_t)w; };
   auto tR = [&](int w) -> uint32_t { return tmem + 384 + 64 * (uint32_t)w; };
@@ -220,77 +220,91 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sdO(st) + h * kBwdQBox, &tm_do, h * 64, q0, bh, bar(B_DO_FULL + st));
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (7u << 16));
-    } else if (warp == 1 && lane == 0 && n_run > 0) {
-      // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 1 && n_run > 0) {
+      // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+      const bool leader = ptx::elect_one();
       bool ok = true;
       // K-major operands advance 32 bytes per k-step inside a 128-byte row and change box after 4 steps;
       // MN-major operands advance 16 rows (2048 bytes) per k-step.
       auto issue_a = [&](int u) {   // S^T = K Q^T -> S[u & 1]
         const uint32_t q = sQ(u % kBwdStages);
+        if (!leader) return;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           ptx::mma_ss(tS(u & 1), ptx::desc_sw128_kmajor(sK + (kk >> 2) * kBwdBox + (kk & 3) * 32),
                       ptx::desc_sw128_kmajor(q + (kk >> 2) * kBwdQBox + (kk & 3) * 32), IDESC_S, kk > 0);
-        ptx::mma_commit(bar(B_S_READY + (u & 1)));
+        if (leader) ptx::mma_commit(bar(B_S_READY + (u & 1)));
       };
       auto issue_b = [&](int u) {   // dP^T = V dO^T -> R[u & 1]
         const uint32_t d = sdO(u % kBwdStages);
+        if (!leader) return;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           ptx::mma_ss(tR(u & 1), ptx::desc_sw128_kmajor(sV + (kk >> 2) * kBwdBox + (kk & 3) * 32),
                       ptx::desc_sw128_kmajor(d + (kk >> 2) * kBwdQBox + (kk & 3) * 32), IDESC_S, kk > 0);
-        ptx::mma_commit(bar(B_DP_READY + (u & 1)));
+        if (leader) ptx::mma_commit(bar(B_DP_READY + (u & 1)));
       };
       auto stage_parity = [](int u) -> uint32_t { return (uint32_t)(u / kBwdStages) & 1u; };
-      ok = ptx::mbar_wait(bar(B_KV_FULL), 0, s_abort) && ptx::mbar_wait(bar(B_Q_FULL), 0, s_abort);
+      ok = ptx::mbar_wait_warp(bar(B_KV_FULL), 0, s_abort) && ptx::mbar_wait_warp(bar(B_Q_FULL), 0, s_abort);
       if (ok) { ptx::tc_fence_after(); issue_a(0); }
-      if (ok) ok = ptx::mbar_wait(bar(B_DO_FULL), 0, s_abort);
+      if (ok) ok = ptx::mbar_wait_warp(bar(B_DO_FULL), 0, s_abort);
       if (ok) { ptx::tc_fence_after(); issue_b(0); }
       for (int u = 0; u < n_run && ok; ++u) {
         const int w = u & 1, st = u % kBwdStages;
         const uint32_t ph = (uint32_t)(u >> 1) & 1u;       // per-warpgroup barriers complete once per own unit
         if (u + 1 < n_run) {
-          ok = ptx::mbar_wait(bar(B_Q_FULL + (u + 1) % kBwdStages), stage_parity(u + 1), s_abort);
+          ok = ptx::mbar_wait_warp(bar(B_Q_FULL + (u + 1) % kBwdStages), stage_parity(u + 1), s_abort);
           if (!ok) break;
           ptx::tc_fence_after();
           issue_a(u + 1);
         }
-        ok = ptx::mbar_wait(bar(B_P_READY + w), ph, s_abort);
+        if (leader) SKB_TR(0, u, 4);
+        ok = ptx::mbar_wait_warp(bar(B_P_READY + w), ph, s_abort);
         if (!ok) break;
+        if (leader) SKB_TR(0, u, 0);
         ptx::tc_fence_after();
         // (c) dV += P^T dO : A = P^T in TMEM (4 k-steps of 16 query rows), B = dO MN-major
+        if (leader)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           ptx::mma_ts(tDV, tS(w) + kk * 8, ptx::desc_sw128_mnmajor(sdO(st) + kk * 2048, kBwdQBox), IDESC_KM,
                       (u > 0) || (kk > 0));
-        ptx::mma_commit(bar(B_DO_EMPTY + st));
+        if (leader) ptx::mma_commit(bar(B_DO_EMPTY + st));
+        if (leader) SKB_TR(0, u, 1);
         if (u + 1 < n_run) {
-          ok = ptx::mbar_wait(bar(B_DO_FULL + (u + 1) % kBwdStages), stage_parity(u + 1), s_abort);
+          ok = ptx::mbar_wait_warp(bar(B_DO_FULL + (u + 1) % kBwdStages), stage_parity(u + 1), s_abort);
           // R[w^1] still holds dQ^T of unit u-1 until that warpgroup has pulled it into registers
-          if (ok && u >= 1) ok = ptx::mbar_wait(bar(B_RP_FREE + (w ^ 1)), (uint32_t)((u - 1) >> 1) & 1u, s_abort);
+          if (leader) SKB_TR(0, u, 6);
+          if (ok && u >= 1) ok = ptx::mbar_wait_warp(bar(B_RP_FREE + (w ^ 1)), (uint32_t)((u - 1) >> 1) & 1u, s_abort);
           if (!ok) break;
+          if (leader) SKB_TR(0, u, 7);
           ptx::tc_fence_after();
           issue_b(u + 1);
+          if (leader) SKB_TR(0, u, 5);
         }
-        ok = ptx::mbar_wait(bar(B_DS_READY + w), ph, s_abort);
+        ok = ptx::mbar_wait_warp(bar(B_DS_READY + w), ph, s_abort);
         if (!ok) break;
+        if (leader) SKB_TR(0, u, 2);
         ptx::tc_fence_after();
         // (d) dK += dS^T Q : A = dS^T (smem, K-major, 4 k-steps), B = Q MN-major
+        if (leader)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           ptx::mma_ss(tDK, ptx::desc_sw128_kmajor(sdS(w) + kk * 32), ptx::desc_sw128_mnmajor(sQ(st) + kk * 2048, kBwdQBox),
                       IDESC_KM, (u > 0) || (kk > 0));
         // (e) dQ^T = K^T dS^T -> R[w] : A = K MN-major (8 k-steps over KV rows), B = dS^T MN-major
+        if (leader)
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           ptx::mma_ss(tR(w), ptx::desc_sw128_mnmajor(sK + kk * 2048, kBwdBox), ptx::desc_sw128_mnmajor(sdS(w) + kk * 2048, kBwdQTile),
                       IDESC_DQ, kk > 0);
-        ptx::mma_commit(bar(B_DQ_DONE + w));
-        ptx::mma_commit(bar(B_Q_EMPTY + st));
+        if (leader) ptx::mma_commit(bar(B_DQ_DONE + w));
+        if (leader) SKB_TR(0, u, 3);
+        if (leader) ptx::mma_commit(bar(B_Q_EMPTY + st));
       }
-      ptx::mma_commit(bar(B_ACC_DONE));
-      if (!ptx::mbar_wait(bar(B_ACC_DONE), 0, s_abort)) ok = false;   // drain before TMEM is released
-      if (!ok) atomicCAS(&g_dev_status, 0u, (8u << 16));
+      if (leader) ptx::mma_commit(bar(B_ACC_DONE));
+      if (!ptx::mbar_wait_warp(bar(B_ACC_DONE), 0, s_abort)) ok = false;   // drain before TMEM is released
+      if (!ok && leader) atomicCAS(&g_dev_status, 0u, (8u << 16));
     }
   } else {
     ptx::setmaxnreg_inc<224>();
@@ -313,6 +327,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
            ptx::mbar_wait(bar(B_S_READY + w), ph, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (wq == 0 && lane == 0) SKB_TR(1 + w, u >> 1, 0);
       ptx::tc_fence_after();
       // visible iff kvidx <= q + shift  <=>  column c >= kvidx - shift - q0
       const int cmin = causal ? kvidx - shift - q0 : -1;
@@ -353,11 +368,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(B_P_READY + w));
+      if (wq == 0 && lane == 0) SKB_TR(1 + w, u >> 1, 1);
 
       // ---- dS^T = P^T o (dP^T - Delta) -> shared memory tile dS[w] (rows = KV, 64 query columns = 128 bytes)
       ok = ptx::mbar_wait(bar(B_DP_READY + w), ph, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (wq == 0 && lane == 0) SKB_TR(1 + w, u >> 1, 2);
       ptx::tc_fence_after();
       {
         uint8_t* ds_row = gbase + (sdS(w) - sbase) + r * 128;
@@ -388,12 +405,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       fence_async_smem();          // make the generic-proxy stores visible to the tensor core
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(B_DS_READY + w));
+      if (wq == 0 && lane == 0) SKB_TR(1 + w, u >> 1, 3);
 
       // ---- drain dQ^T (lane = d, columns = query rows): pull it into registers, release the TMEM buffer,
       //      then add into the fp32 accumulator; each warp instruction covers 128 contiguous bytes.
       ok = ptx::mbar_wait(bar(B_DQ_DONE + w), ph, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (wq == 0 && lane == 0) SKB_TR(1 + w, u >> 1, 4);
       ptx::tc_fence_after();
       {
         uint32_t qa[32], qb[32];
@@ -410,6 +429,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int c = 0; c < 32; ++c)
           if (q0 + 32 + c < Sq) red_add(dst + (size_t)(32 + c) * HD, __uint_as_float(qb[c]));
       }
+      if (wq == 0 && lane == 0) SKB_TR(1 + w, u >> 1, 5);
     }
 
     // ------------------------------------------------------------------ epilogue: dK, dV

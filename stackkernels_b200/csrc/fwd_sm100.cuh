@@ -128,7 +128,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
-  const uint32_t tmem = *s_tmem;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, *s_tmem, 0);
 
   if (warp < 4) {
     ptx::setmaxnreg_dec<56>();
@@ -164,10 +164,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         load_kv(&tm_v, sV, V_FULL, j);
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (1u << 16));
-    } else if (warp == 1 && lane == 0) {
-      // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+      const bool leader = ptx::elect_one();
       bool ok = true;
       auto issue_qk = [&](int t, int st) {
+        if (!leader) return;
 #pragma unroll
         for (int kk = 0; kk < KSTEPS_QK; ++kk) {
           const uint32_t off = (uint32_t)(kk / 4) * kBoxBytes + (uint32_t)(kk % 4) * 32u;
@@ -176,55 +178,56 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
       };
       auto issue_pv = [&](int t, int st, int j) {
+        if (!leader) return;
 #pragma unroll
         for (int kk = 0; kk < KSTEPS_PV; ++kk)
           ptx::mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
                       ptx::desc_sw128_mnmajor(sV + st * TILE + kk * 2048, kBoxBytes), IDESC_PV, (j > 0) || (kk > 0));
       };
       if (nmax > 0) {
-        ok = ptx::mbar_wait(bar(K_FULL), 0, s_abort);
+        ok = ptx::mbar_wait_warp(bar(K_FULL), 0, s_abort);
         for (int t = 0; t < 2 && ok; ++t) {
           if (ntile[t] > 0) {
-            ok = ptx::mbar_wait(bar(Q_FULL + t), 0, s_abort);
+            ok = ptx::mbar_wait_warp(bar(Q_FULL + t), 0, s_abort);
             if (!ok) break;
             ptx::tc_fence_after();
             issue_qk(t, 0);
-            ptx::mma_commit(bar(S_FULL + t));
+            if (leader) ptx::mma_commit(bar(S_FULL + t));
           }
         }
-        if (ok) ptx::mma_commit(bar(K_EMPTY));
+        if (ok) if (leader) ptx::mma_commit(bar(K_EMPTY));
       }
       for (int j = 0; j < nmax && ok; ++j) {
         const int st = j % kStages, stn = (j + 1) % kStages;
         const uint32_t ph = (uint32_t)(j / kStages) & 1u, phn = (uint32_t)((j + 1) / kStages) & 1u;
-        ok = ptx::mbar_wait(bar(V_FULL + st), ph, s_abort);
-        SKB_TR(0, j, 0);
+        ok = ptx::mbar_wait_warp(bar(V_FULL + st), ph, s_abort);
+        if (leader) SKB_TR(0, j, 0);
         for (int t = 0; t < 2 && ok; ++t) {
           if (j < ntile[t]) {
-            ok = ptx::mbar_wait(bar(P_FULL + t), (uint32_t)j & 1u, s_abort);
+            ok = ptx::mbar_wait_warp(bar(P_FULL + t), (uint32_t)j & 1u, s_abort);
             if (!ok) break;
-            SKB_TR(0, j, 1 + 3 * t);
+            if (leader) SKB_TR(0, j, 1 + 3 * t);
             ptx::tc_fence_after();
             issue_pv(t, st, j);
-            SKB_TR(0, j, 2 + 3 * t);
-            if (j == ntile[t] - 1) ptx::mma_commit(bar(O_DONE + t));
+            if (leader) SKB_TR(0, j, 2 + 3 * t);
+            if (j == ntile[t] - 1) if (leader) ptx::mma_commit(bar(O_DONE + t));
           }
-          if (t == 1) ptx::mma_commit(bar(V_EMPTY + st));
+          if (t == 1) if (leader) ptx::mma_commit(bar(V_EMPTY + st));
           if (j + 1 < ntile[t]) {
-            ok = ptx::mbar_wait(bar(K_FULL + stn), phn, s_abort);
+            ok = ptx::mbar_wait_warp(bar(K_FULL + stn), phn, s_abort);
             if (!ok) break;
             ptx::tc_fence_after();
             issue_qk(t, stn);
-            ptx::mma_commit(bar(S_FULL + t));
-            SKB_TR(0, j, 3 + 3 * t);
+            if (leader) ptx::mma_commit(bar(S_FULL + t));
+            if (leader) SKB_TR(0, j, 3 + 3 * t);
           }
-          if (t == 1 && j + 1 < nmax) ptx::mma_commit(bar(K_EMPTY + stn));
+          if (t == 1 && j + 1 < nmax) if (leader) ptx::mma_commit(bar(K_EMPTY + stn));
         }
       }
       // Drain: nothing of this CTA's tensor-core work may be in flight when TMEM is released.
-      ptx::mma_commit(bar(DRAIN));
-      if (!ptx::mbar_wait(bar(DRAIN), 0, s_abort)) ok = false;
-      if (!ok) atomicCAS(&g_dev_status, 0u, (2u << 16));
+      if (leader) ptx::mma_commit(bar(DRAIN));
+      if (!ptx::mbar_wait_warp(bar(DRAIN), 0, s_abort)) ok = false;
+      if (!ok && leader) atomicCAS(&g_dev_status, 0u, (2u << 16));
     }
   } else {
     ptx::setmaxnreg_inc<224>();
@@ -277,24 +280,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       const float mref = (m == -INFINITY) ? 0.f : m;
       if (wq == 0 && lane == 0) SKB_TR(1 + t, j, 2);
-      // Exponentials: of every four, two go to the MUFU unit and two to the FMA pipe (exp2_poly2),
-      // with the scale/subtract and the row sums done two lanes at a time.
+      // Exponentials: of every eight, six go to the MUFU unit and two to the FMA pipe (exp2_poly2): with
+      // 16 MUFU results per clock per SM the exponentials alone would take as long as the tile's MMAs,
+      // and a larger FMA share would make instruction issue the limit instead.
       const uint64_t sc2 = ptx::f2_pack(scale_log2, scale_log2), nm2 = ptx::f2_pack(-mref, -mref);
       uint64_t sumA = ptx::f2_pack(0.f, 0.f), sumB = sumA;
 #pragma unroll
-      for (int c = 0; c < 128; c += 4) {
-        const uint64_t xa = ptx::f2_fma(ptx::f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nm2);
-        const uint64_t xb = ptx::f2_fma(ptx::f2_pack(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2, nm2);
-        float x0, x1, x2, x3, p0, p1, p2, p3;
-        ptx::f2_unpack(xa, x0, x1);
-        ptx::f2_unpack(xb, x2, x3);
-        p0 = ptx::ex2(x0);
-        p1 = ptx::ex2(x1);
-        ptx::exp2_poly2(x2, x3, p2, p3);
-        sumA = ptx::f2_add(sumA, ptx::f2_pack(p0, p1));
-        sumB = ptx::f2_add(sumB, ptx::f2_pack(p2, p3));
-        sr[c >> 1] = pack2(p0, p1, T());
-        sr[(c >> 1) + 1] = pack2(p2, p3, T());
+      for (int c = 0; c < 128; c += 8) {
+        float x[8], pe[8];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2)
+          ptx::f2_unpack(ptx::f2_fma(ptx::f2_pack(__uint_as_float(sr[c + e]), __uint_as_float(sr[c + e + 1])), sc2, nm2),
+                         x[e], x[e + 1]);
+#pragma unroll
+        for (int e = 0; e < 6; ++e) pe[e] = ptx::ex2(x[e]);
+        ptx::exp2_poly2(x[6], x[7], pe[6], pe[7]);
+        sumA = ptx::f2_add(sumA, ptx::f2_add(ptx::f2_pack(pe[0], pe[1]), ptx::f2_pack(pe[2], pe[3])));
+        sumB = ptx::f2_add(sumB, ptx::f2_add(ptx::f2_pack(pe[4], pe[5]), ptx::f2_pack(pe[6], pe[7])));
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) sr[(c + e) >> 1] = pack2(pe[e], pe[e + 1], T());
       }
       {
         float a0, a1, b0, b1;

@@ -8,6 +8,7 @@
 
 #include "decode_group.cuh"
 #include "bwd_sm100.cuh"
+#include "fwd2_sm100.cuh"
 #include "general_kernels.cuh"
 #include "skb200.h"
 
@@ -195,6 +196,22 @@ int launch_fwd_sm100(const void* q, const void* k, const void* v, void* o, float
   return SKB_OK;
 }
 
+template <typename T>
+int launch_fwd2_sm100(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
+                      int Sk, int causal, float scale, cudaStream_t st) {
+  CUtensorMap mk, mv;
+  const int dt = DtypeOf<T>::value;
+  if (int rc = make_map_3d(&mk, dt, k, 128, Sk, (size_t)B * Hkv)) return rc;
+  if (int rc = make_map_3d(&mv, dt, v, 128, Sk, (size_t)B * Hkv)) return rc;
+  auto kern = sm100::fwd2_kernel<T>;
+  if (int rc = set_smem(kern, sm100::kF2SmemBytes)) return rc;
+  dim3 grid(cdiv(Sq, 128), Hq, B);
+  kern<<<grid, sm100::kF2Threads, sm100::kF2SmemBytes, st>>>((const T*)q, mk, mv, (T*)o, lse, Hq, Hkv, Sq, Sk, causal,
+                                                            scale * kLog2e);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // ------------------------------------------------------------------------------------ tensor-core backward
@@ -348,8 +365,14 @@ int skb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SKB_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
   const bool covers = fwd_sm100_covers(D, dtype, scale);
-  if (impl == SKB_IMPL_SM100 && !covers) return SKB_ERR_UNSUPPORTED;
+  if ((impl == SKB_IMPL_SM100 || impl == 3) && !covers) return SKB_ERR_UNSUPPORTED;
+  const bool gen2 = impl == 3;   // selector for the alternative forward (Q resident in TMEM, fwd2_sm100.cuh), for A/B timing
+  if (gen2) impl = SKB_IMPL_SM100;
   const bool use_tc = impl == SKB_IMPL_SM100 || (impl == SKB_IMPL_AUTO && covers && Sq >= 128 && Sk >= 128);
+  if (use_tc && D == 128 && gen2) {
+    if (dtype == SKB_F16) return launch_fwd2_sm100<__half>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
+    return launch_fwd2_sm100<__nv_bfloat16>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
+  }
   if (use_tc) {
     if (dtype == SKB_F16)
       return D == 64 ? launch_fwd_sm100<__half, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st)

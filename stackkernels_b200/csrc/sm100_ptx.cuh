@@ -56,6 +56,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Warp-collective bounded wait: every lane polls, the verdict is made uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+// One lane of a converged warp.  tcgen05.mma / commit take their descriptors from uniform registers; an
+// issuer that runs as a whole converged warp (loop counters, addresses and descriptors provably
+// warp-uniform) with only the instruction itself predicated on this lane issues an MMA every few clocks,
+// whereas a single diverged lane needs vector->uniform register moves for every instruction (measured on
+// B200: ~95 clocks per MMA instruction against 64 clocks of execution for a 128x128x16 MMA).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t p;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(p));
+  return p != 0;
+}
+
 // ---------------------------------------------------------------- TMA (tiled, 3-D, no multicast)
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
