@@ -41,6 +41,19 @@ WORKLOADS = {
 DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel per launch, from the ncu
+# captures summarised under profiles/ (taken on a smaller case of the same kernel and scaled by the units).
+NCU_TRAFFIC_BYTES = {
+    "prefill_fwd_c2": 4 * 251.0e6,        # profiles/fwd_sm100_prefill_bf16_d128.md
+    "prefill_fwd_profile": 251.0e6,
+    "fwdbwd_c3": 4 * 1136.6e6,            # profiles/bwd_sm100_bf16_d128.md
+    "bwd_profile": 1136.6e6,
+    "decode_c4": 8 * 855.5e6,             # profiles/decode_group_bf16_d128.md
+    "decode_profile": 855.5e6,
+    "decode_c5": 1.0757e9,
+}
+
+
 def load_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -267,7 +280,7 @@ def run_native(args):
                    "per_gpu": "one full-size shard per GPU, units = (batch x kv-head group), no collective",
                    "l2": "inputs_exceed_l2"},
         "roofline": {"bound": "hbm" if is_decode else "tensor", "achieved": achieved, "peak": peak, "unit": unit,
-                     "frac": achieved / peak, "traffic": None,
+                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(name),
                      "peak_source": f"{peaks['src']} ({'copy bandwidth' if is_decode else ('bf16 sustained' if long_region else 'bf16 burst')})",
                      "frac_of_burst": None if is_decode else achieved / peaks["tf"],
                      "frac_of_sustained": None if is_decode else achieved / peaks["tf_sus"]},
