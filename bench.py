@@ -177,7 +177,7 @@ def time_steps(fn, steps, warmup):
 def run_native(args):
     import torch.distributed as dist
     from stackkernels_b200 import _lib
-    from stackkernels_b200 import flash_attention, flash_decode
+    from stackkernels_b200 import flash_attention, flash_attention_host, flash_decode
     from stackkernels_b200.launchers import flash_attn_bwd, flash_attn_fwd
     from stackkernels_b200.launchers import flash_decode as core_decode
 
@@ -230,10 +230,13 @@ def run_native(args):
         if with_e2e:
             # end to end through the public API: host (pinned) -> device, compute, result -> host
             def e2e_step():
-                dd = [t.to(dev, non_blocking=True) if not t.is_cuda else t for t in host]
                 if kind == "fwd":
-                    out = flash_attention(dd[0], dd[1], dd[2], causal=True)
-                elif kind == "decode":
+                    # host q, k, v -> chunked H2D / kernel / D2H pipeline -> host O
+                    flash_attention_host(host[0], host[1], host[2], out=out_host, causal=True)
+                    torch.cuda.current_stream().synchronize()
+                    return out_host
+                dd = [t.to(dev, non_blocking=True) if not t.is_cuda else t for t in host]
+                if kind == "decode":
                     out = flash_decode(dd[0], dd[1], dd[2], cache_seqlens=lens_d)
                 else:
                     raise NotImplementedError

@@ -182,3 +182,22 @@ def test_module_and_decode_start_pos(skb):
         skb.flash_decode(q.cuda(), k.cuda(), v.cuda())            # q_len != 1
     with pytest.raises(ValueError):
         skb.flash_attention(q.cuda(), k.cuda()[:, :, :, :32], v.cuda())
+
+
+def test_host_buffer_pipeline_matches_oracle(skb):
+    """flash_attention_host: chunked H2D / kernel / D2H pipeline over host tensors (ragged last chunk)."""
+    from oracle import attention_oracle as orc
+    torch.manual_seed(61)
+    B, Hq, Hkv, S, D = 5, 4, 2, 256, 128
+    q = torch.randn(B, Hq, S, D).bfloat16().pin_memory()
+    k = torch.randn(B, Hkv, S, D).bfloat16().pin_memory()
+    v = torch.randn(B, Hkv, S, D).bfloat16().pin_memory()
+    out, lse = skb.flash_attention_host(q, k, v, causal=True, chunk_rows=2, return_lse=True)
+    torch.cuda.synchronize()
+    eo, el = orc.attention_forward(q, k, v, causal=True)
+    assert not out.is_cuda and out.is_pinned()
+    assert_parity(out, eo, "bf16", "host O")
+    assert_parity(lse, el, "bf16", "host LSE")
+    out2 = skb.flash_attention_host(q, k, v, causal=True)          # default chunking, fresh output buffer
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
