@@ -35,6 +35,8 @@ WORKLOADS = {
     "decode_profile": ("decode", dict(B=8, Hq=32, Hkv=8, cap=32768, D=128, dtype="bf16", seed=3, lens="uniform")),
     "prefill_fwd_s8192": ("fwd", dict(B=4, Hq=64, Hkv=8, S=8192, D=128, dtype="bf16", seed=2)),
     "fwdbwd_c3": ("bwd", dict(B=4, Hq=64, Hkv=8, S=8192, D=128, dtype="bf16", seed=2)),
+    # RoPE on the query tensor of config 3, (B,S,H,D) layout, positions from 0: bytes = read + write of x
+    "rope_c3": ("rope", dict(B=4, H=64, S=8192, D=128, dtype="bf16", seed=2)),
     "decode_c4": ("decode", dict(B=64, Hq=32, Hkv=8, cap=32768, D=128, dtype="bf16", seed=3, lens="uniform")),
     "decode_c5": ("decode", dict(B=16, Hq=64, Hkv=1, cap=131072, D=128, dtype="fp16", seed=4, lens="full", std=0.5)),
 }
@@ -125,6 +127,8 @@ def make_inputs(kind, p, device, pinned_host=False):
 
     def draw(*shape):
         return (torch.randn(*shape, dtype=torch.float32) * std).to(dt)
+    if kind == "rope":
+        return [draw(p["B"], p["S"], p["H"], p["D"])], None
     if kind in ("fwd", "bwd"):
         host = [draw(p["B"], p["Hq"], p["S"], p["D"]), draw(p["B"], p["Hkv"], p["S"], p["D"]),
                 draw(p["B"], p["Hkv"], p["S"], p["D"])]
@@ -150,6 +154,8 @@ def make_inputs(kind, p, device, pinned_host=False):
 
 def work_units(kind, p, lens=None):
     """Algorithmic work of one step on one GPU: FLOPs (prefill/backward) or KV bytes (decode)."""
+    if kind == "rope":
+        return 2.0 * p["B"] * p["S"] * p["H"] * p["D"] * (2 if p["dtype"] != "fp32" else 4)
     if kind == "fwd":
         return 2.0 * p["B"] * p["Hq"] * p["S"] ** 2 * p["D"]             # causal half of 4*B*H*S^2*D
     if kind == "bwd":
@@ -199,7 +205,11 @@ def run_native(args):
         d = [t.to(dev, non_blocking=True) for t in host]
         lens_d = None if lens is None else lens.to(dev)
         launches = 1
-        if kind == "fwd":
+        if kind == "rope":
+            from stackkernels_b200.embedding import precompute_freqs, rope_launch
+            cos, sin = precompute_freqs(p["D"], p["S"], device=dev)
+            fn = lambda: rope_launch(d[0], cos, sin, 0)
+        elif kind == "fwd":
             fn = lambda: flash_attn_fwd(d[0], d[1], d[2], is_causal=True)
         elif kind == "bwd":
             o, lse = flash_attn_fwd(d[0], d[1], d[2], is_causal=True)
@@ -267,7 +277,7 @@ def run_native(args):
     name = args.workload
     r = measure(name, args.steps, args.warmup, with_e2e=not args.no_e2e)
     kind, p = r["kind"], r["p"]
-    is_decode = kind == "decode"
+    is_decode = kind in ("decode", "rope")          # bandwidth-bound workloads report GB/s
     scale = 1e-9 if is_decode else 1e-12
     unit = "GB/s" if is_decode else "TFLOP/s"
     value = world * r["units"] * scale / (r["ms_step"] * 1e-3)
@@ -275,7 +285,8 @@ def run_native(args):
     long_region = r["ms_step"] * args.steps > 1000.0      # seconds-long loops run under the power cap
     peak = peaks["hbm"] if is_decode else (peaks["tf_sus"] if long_region else peaks["tf"])
     line = {
-        "metric": {"fwd": "attn_fwd_tflops", "bwd": "attn_bwd_tflops", "decode": "flash_decode_hbm_gbs"}[kind],
+        "metric": {"fwd": "attn_fwd_tflops", "bwd": "attn_bwd_tflops", "decode": "flash_decode_hbm_gbs",
+                   "rope": "rope_hbm_gbs"}[kind],
         "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": r["ms_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": p["dtype"], "data": "synthetic",
@@ -296,12 +307,12 @@ def run_native(args):
         line["cpu_baseline"] = cpu_baseline(name, budget_s=args.cpu_seconds)
     if world == 1 and not args.no_extras:
         extras = {}
-        for en, st in (("prefill_fwd_s8192", 5), ("fwdbwd_c3", 2), ("decode_c4", 10), ("decode_c5", 10)):
+        for en, st in (("prefill_fwd_s8192", 5), ("fwdbwd_c3", 2), ("decode_c4", 10), ("decode_c5", 10), ("rope_c3", 10)):
             if en == name:
                 continue
             torch.cuda.empty_cache()
             e = measure(en, st, 3, with_e2e=False)
-            dec = e["kind"] == "decode"
+            dec = e["kind"] in ("decode", "rope")
             sc = 1e-9 if dec else 1e-12
             a = e["units"] * sc / (e["ms_step"] * 1e-3)
             pk = peaks["hbm"] if dec else peaks["tf"]

@@ -125,6 +125,26 @@ int skb_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, 
                        int B, int Hq, int Hkv, int Scap, int D,
                        int dtype, float scale, int num_splits, void* stream);
 
+/* Rotary position embedding with a start position -- the op applied to q and k right before attention.
+ * Replaces the RoPE launchers (src/stackkernels/_core/positional/rope.py:140-172; semantics of
+ * src/stackkernels/_reference/torch/rope.py:41-59 forward and src/stackkernels/torch/embedding.py:46-64
+ * backward).  x, out: (B,S,H,D); cos/sin tables: (max_seq, D) of `table_dtype` (SKB_F32 or the dtype of x);
+ * positions start_pos .. start_pos+S-1.  backward != 0 applies the gradient formula to x = dy.
+ * out_bhsd != 0 writes the result as (B,H,S,D), the layout skb_attn_fwd takes.  D/2 must be a multiple of
+ * 8 (16-bit) or 4 (fp32). */
+int skb_rope(const void* x, const void* cos_table, const void* sin_table, void* out,
+             int B, int S, int H, int D, int dtype, int table_dtype,
+             int start_pos, int max_seq, int backward, int out_bhsd, void* stream);
+
+/* In-place KV-cache append: cache[b, h, len_b + t, :] = new[b, h, t, :], t < T_new, for K and V, where
+ * len_b = cache_seqlens[b] (device int32, clamped to [0, Scap]) or `fixed_len` when cache_seqlens is NULL.
+ * Rows that would pass the capacity are dropped.  advance != 0 then sets cache_seqlens[b] =
+ * min(len_b + T_new, Scap) on the same stream, ready for skb_decode.  k_new, v_new: (B,Hkv,T_new,D);
+ * caches: (B,Hkv,Scap,D).  The reference reserves this op without implementing it
+ * (src/stackkernels/_core/cache/kv_update.py:1-3). */
+int skb_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, int32_t* cache_seqlens,
+                  int fixed_len, int advance, int B, int Hkv, int T_new, int Scap, int D, int dtype, void* stream);
+
 /* Human-readable text for a status code; mirrors the messages of validate_attention_layout
  * (src/stackkernels/_opt/memory/layout.py:19-39). */
 const char* skb_status_string(int status);

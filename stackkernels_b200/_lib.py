@@ -32,6 +32,8 @@ SIGNATURES = {
     "skb_decode_workspace_bytes": (_sz, [_i] * 7),
     "skb_decode": (_i, [_vp] * 6 + [_i] * 5 + [_i, _f, _i, _i, _vp, _sz, _vp]),
     "skb_decode_noalloc": (_i, [_vp] * 6 + [_i] * 5 + [_i, _f, _i, _vp]),
+    "skb_rope": (_i, [_vp] * 4 + [_i] * 10 + [_vp]),
+    "skb_kv_append": (_i, [_vp] * 5 + [_i] * 8 + [_vp]),
     "skb_status_string": (_c.c_char_p, [_i]),
     "skb_last_cuda_error": (_c.c_char_p, []),
     "skb_version": (_i, []),

@@ -9,6 +9,7 @@
 #include "decode_group.cuh"
 #include "bwd_sm100.cuh"
 #include "fwd2_sm100.cuh"
+#include "aux_kernels.cuh"
 #include "general_kernels.cuh"
 #include "skb200.h"
 
@@ -506,6 +507,56 @@ int skb_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, 
     case SKB_F16: return decode_general<__half>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
     default: return decode_general<__nv_bfloat16>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
   }
+}
+
+int skb_rope(const void* x, const void* cos_table, const void* sin_table, void* out, int B, int S, int H, int D,
+             int dtype, int table_dtype, int start_pos, int max_seq, int backward, int out_bhsd, void* stream) {
+  if (!x || !cos_table || !sin_table || !out) return SKB_ERR_NULL;
+  if (dtype != SKB_F32 && dtype != SKB_F16 && dtype != SKB_BF16) return SKB_ERR_DTYPE;
+  if (table_dtype != SKB_F32 && table_dtype != dtype) return SKB_ERR_DTYPE;
+  if (B < 1 || S < 1 || H < 1 || start_pos < 0 || start_pos + S > max_seq) return SKB_ERR_SHAPE;
+  const int ve = dtype == SKB_F32 ? 4 : 8;
+  if (D < 2 || D % 2 != 0 || (D / 2) % ve != 0) return SKB_ERR_HEAD_DIM;
+  if (!aligned16(x) || !aligned16(out)) return SKB_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D / 2 / ve > 256 || (size_t)B * S > 0x7fffffffull) return SKB_ERR_TOO_LARGE;
+  if (!aligned16(cos_table) || !aligned16(sin_table)) return SKB_ERR_ALIGN;
+  const unsigned blocks = (unsigned)((size_t)B * S);
+#define SKB_ROPE(T_, TT_)                                                                                         \
+  aux::rope_kernel<T_, TT_><<<blocks, 256, 0, st>>>((const T_*)x, (const TT_*)cos_table, (const TT_*)sin_table,   \
+                                                    (T_*)out, S, H, D, start_pos, backward, out_bhsd)
+  if (dtype == SKB_F32) SKB_ROPE(float, float);
+  else if (dtype == SKB_F16) { if (table_dtype == SKB_F32) SKB_ROPE(__half, float); else SKB_ROPE(__half, __half); }
+  else { if (table_dtype == SKB_F32) SKB_ROPE(__nv_bfloat16, float); else SKB_ROPE(__nv_bfloat16, __nv_bfloat16); }
+#undef SKB_ROPE
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
+int skb_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, int32_t* cache_seqlens,
+                  int fixed_len, int advance, int B, int Hkv, int T_new, int Scap, int D, int dtype, void* stream) {
+  if (!k_new || !v_new || !k_cache || !v_cache) return SKB_ERR_NULL;
+  if (dtype != SKB_F32 && dtype != SKB_F16 && dtype != SKB_BF16) return SKB_ERR_DTYPE;
+  if (B < 1 || Hkv < 1 || T_new < 1 || Scap < 1) return SKB_ERR_SHAPE;
+  if (!cache_seqlens && (fixed_len < 0 || fixed_len > Scap)) return SKB_ERR_SHAPE;
+  const int ve = dtype == SKB_F32 ? 4 : 8;
+  if (D < 1 || D % ve != 0) return SKB_ERR_HEAD_DIM;
+  if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_cache) || !aligned16(v_cache)) return SKB_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t n_vec = (size_t)B * Hkv * T_new * (D / ve);
+  const unsigned blocks = (unsigned)((n_vec + 255) / 256);
+  if (dtype == SKB_F32)
+    aux::kv_append_kernel<float><<<blocks, 256, 0, st>>>((const float*)k_new, (const float*)v_new, (float*)k_cache,
+                                                         (float*)v_cache, cache_seqlens, fixed_len, Hkv, T_new, Scap, D, n_vec);
+  else   // 16-bit types are copied bit for bit
+    aux::kv_append_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)k_new, (const __half*)v_new, (__half*)k_cache,
+                                                          (__half*)v_cache, cache_seqlens, fixed_len, Hkv, T_new, Scap, D, n_vec);
+  SKB_CUDA(cudaGetLastError());
+  if (advance && cache_seqlens) {
+    aux::kv_advance_kernel<<<(B + 127) / 128, 128, 0, st>>>(cache_seqlens, B, T_new, Scap);
+    SKB_CUDA(cudaGetLastError());
+  }
+  return SKB_OK;
 }
 
 #ifdef SKB_TRACE

@@ -1,0 +1,114 @@
+"""Rotary position embedding: drop-in for ``stackkernels.torch.embedding``
+(``src/stackkernels/torch/embedding.py`` in the reference): ``apply_rope``, ``RoPE``, ``RoPEFunction`` and
+``precompute_freqs`` with the same signatures; compute in ``libskb200.so`` (``skb_rope``)."""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from .launchers import _DTYPES, _raise_for_status, _stream
+
+
+def precompute_freqs(dim: int, max_seq_len: int = 4096, base: float = 10000.0, device="cpu",
+                     dtype: torch.dtype = torch.float32):
+    """cos/sin tables of shape (max_seq_len, dim), as ``_reference/torch/rope.py:6-29`` builds them."""
+    half_dim = dim // 2
+    inv_freq = 1.0 / (base ** (torch.arange(0, half_dim, dtype=torch.float32, device=device) / half_dim))
+    t = torch.arange(max_seq_len, dtype=torch.float32, device=device)
+    freqs = torch.outer(t, inv_freq)
+    cos_half, sin_half = torch.cos(freqs), torch.sin(freqs)
+    return torch.cat([cos_half, cos_half], dim=-1).to(dtype), torch.cat([sin_half, sin_half], dim=-1).to(dtype)
+
+
+def rope_launch(x, cos, sin, start_pos: int = 0, backward: bool = False, out_bhsd: bool = False):
+    """One ``skb_rope`` call.  x ``(B,S,H,D)`` CUDA tensor; returns a new tensor (``(B,H,S,D)`` with out_bhsd)."""
+    if x.ndim != 4:
+        raise ValueError(f"Expected a 4D tensor (B, S, H, D), got {x.ndim}D")
+    if not x.is_cuda:
+        raise RuntimeError("stackkernels_b200 runs on CUDA tensors only: there is no CPU fallback on this path")
+    if x.dtype not in _DTYPES:
+        raise ValueError(f"Unsupported dtype {x.dtype}")
+    B, S, H, D = x.shape
+    if cos.shape != sin.shape or cos.ndim != 2 or cos.shape[1] != D:
+        raise ValueError(f"cos/sin tables must have shape (max_seq_len, {D}), got {tuple(cos.shape)} / {tuple(sin.shape)}")
+    x = x.contiguous()
+    tdt = torch.float32 if cos.dtype == torch.float32 else x.dtype
+    cos = cos.to(device=x.device, dtype=tdt).contiguous()
+    sin = sin.to(device=x.device, dtype=tdt).contiguous()
+    out = torch.empty((B, H, S, D) if out_bhsd else (B, S, H, D), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().skb_rope(x.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), B, S, H, D,
+                                  _DTYPES[x.dtype], _DTYPES[tdt], int(start_pos), int(cos.shape[0]), int(backward),
+                                  int(out_bhsd), _stream(x))
+    _raise_for_status(rc, "apply_rope")
+    return out
+
+
+class RoPEFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, x, cos, sin, start_pos: int = 0):
+        ctx.save_for_backward(cos, sin)
+        ctx.start_pos = start_pos
+        return rope_launch(x, cos, sin, start_pos)
+
+    @staticmethod
+    def backward(ctx: Any, dy):
+        cos, sin = ctx.saved_tensors
+        return rope_launch(dy, cos, sin, ctx.start_pos, backward=True), None, None, None
+
+
+def apply_rope(q, k=None, cos=None, sin=None, start_pos: int = 0):
+    """Rotate q (and optionally k, whose head count may differ) — ``torch/embedding.py:67-105`` of the reference."""
+    dim, seq_len = q.shape[-1], q.shape[1]
+    if cos is None or sin is None:
+        cos, sin = precompute_freqs(dim=dim, max_seq_len=start_pos + seq_len + 128, device=q.device, dtype=q.dtype)
+    q_rot = RoPEFunction.apply(q, cos, sin, start_pos)
+    if k is not None:
+        return q_rot, RoPEFunction.apply(k, cos, sin, start_pos)
+    return q_rot
+
+
+class RoPE(nn.Module):
+    """Module caching the frequency tables (``torch/embedding.py:108-150`` of the reference)."""
+
+    def __init__(self, dim: int, max_seq_len: int = 4096, base: float = 10000.0, device: Any = None) -> None:
+        super().__init__()
+        self.dim, self.max_seq_len, self.base = dim, max_seq_len, base
+        cos, sin = precompute_freqs(dim=dim, max_seq_len=max_seq_len, base=base, device=device or "cpu")
+        self.register_buffer("cos", cos, persistent=False)
+        self.register_buffer("sin", sin, persistent=False)
+
+    def forward(self, q, k=None, start_pos: int = 0):
+        return apply_rope(q, k, self.cos, self.sin, start_pos=start_pos)
+
+
+def kv_cache_append(k_cache, v_cache, k_new, v_new, cache_seqlens=None, start_pos=None, advance: bool = True):
+    """Write the new tokens' K/V rows into the caches in place, at ``cache_seqlens[b]`` per sequence (int32 CUDA
+    tensor, advanced by the number of new tokens when ``advance``) or at the fixed row ``start_pos``.
+    Caches ``(B,H_kv,capacity,D)``, new rows ``(B,H_kv,T,D)``.  Returns ``cache_seqlens`` (or None)."""
+    if k_cache.ndim != 4 or k_new.ndim != 4 or k_cache.shape != v_cache.shape or k_new.shape != v_new.shape:
+        raise ValueError("expected caches (B,H_kv,capacity,D) and new rows (B,H_kv,T,D), K and V alike")
+    B, Hkv, cap, D = k_cache.shape
+    if k_new.shape[0] != B or k_new.shape[1] != Hkv or k_new.shape[3] != D:
+        raise ValueError(f"new rows {tuple(k_new.shape)} do not match caches {tuple(k_cache.shape)}")
+    if not (k_cache.is_cuda and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise RuntimeError("caches must be contiguous CUDA tensors (they are updated in place)")
+    if (cache_seqlens is None) == (start_pos is None):
+        raise TypeError("give exactly one of cache_seqlens and start_pos")
+    if k_cache.dtype not in _DTYPES or k_new.dtype != k_cache.dtype:
+        raise ValueError("caches and new rows must share one supported dtype")
+    k_new, v_new = k_new.contiguous(), v_new.contiguous()
+    lens_ptr = None
+    if cache_seqlens is not None:
+        if cache_seqlens.dtype != torch.int32 or not cache_seqlens.is_cuda or tuple(cache_seqlens.shape) != (B,):
+            raise ValueError(f"cache_seqlens must be an int32 CUDA tensor of shape ({B},)")
+        lens_ptr = cache_seqlens.data_ptr()
+    with torch.cuda.device(k_cache.device):
+        rc = _lib.load().skb_kv_append(k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), lens_ptr,
+                                       int(start_pos or 0), int(advance), B, Hkv, k_new.shape[2], cap, D,
+                                       _DTYPES[k_cache.dtype], _stream(k_cache))
+    _raise_for_status(rc, "kv_cache_append")
+    return cache_seqlens

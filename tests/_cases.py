@@ -71,6 +71,33 @@ DECODE_CASES.update({
 })
 
 
+# RoPE: x (B,S,H,D); the reference's own test shapes plus 16-bit / larger cases.  table: dtype of the cos/sin tables.
+ROPE_CASES = {}
+for _sp in (0, 15, 64):
+    for _dt in ("fp32", "fp16"):
+        ROPE_CASES[f"ref_sp{_sp}_{_dt}"] = dict(B=2, S=8, H=4, D=64, dtype=_dt, table=_dt, start_pos=_sp, seed=42)
+ROPE_CASES.update({
+    "gqa_q_sp23": dict(B=2, S=8, H=16, D=128, dtype="fp32", table="fp32", start_pos=23, seed=43),
+    "gqa_k_sp23": dict(B=2, S=8, H=4, D=128, dtype="fp32", table="fp32", start_pos=23, seed=44),
+    "bf16_s96_d128_sp1000": dict(B=1, S=96, H=6, D=128, dtype="bf16", table="fp32", start_pos=1000, seed=45),
+    "bf16_tab16_d64": dict(B=2, S=33, H=3, D=64, dtype="bf16", table="bf16", start_pos=7, seed=46),
+    "fp16_d256": dict(B=1, S=17, H=2, D=256, dtype="fp16", table="fp32", start_pos=0, seed=47),
+})
+
+
+def make_rope_inputs(c):
+    """x, dy, cos, sin (tables built by the formula of the reference's precompute_freqs)."""
+    torch.manual_seed(c["seed"])
+    x = torch.randn(c["B"], c["S"], c["H"], c["D"], dtype=torch.float32).to(DT[c["dtype"]])
+    dy = torch.randn(c["B"], c["S"], c["H"], c["D"], dtype=torch.float32).to(DT[c["dtype"]])
+    half = c["D"] // 2
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, half, dtype=torch.float32) / half))
+    freqs = torch.outer(torch.arange(c["start_pos"] + c["S"] + 64, dtype=torch.float32), inv_freq)
+    cos = torch.cat([torch.cos(freqs)] * 2, -1).to(DT[c["table"]])
+    sin = torch.cat([torch.sin(freqs)] * 2, -1).to(DT[c["table"]])
+    return x, dy, cos, sin
+
+
 def _draw(shape, c):
     return (torch.randn(*shape, dtype=torch.float32) * c["std"]).to(DT[c["dtype"]])
 

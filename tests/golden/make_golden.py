@@ -19,7 +19,8 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))          # tests/
 from _cases import (FWD_CASES, BWD_CASES, DECODE_CASES, make_fwd_inputs, make_bwd_inputs,  # noqa: E402
-                    make_decode_inputs, config1_inputs, input_checksum, to_np, ROWSTEP)
+                    make_decode_inputs, config1_inputs, input_checksum, to_np, ROWSTEP,
+                    ROPE_CASES, make_rope_inputs)
 
 ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
 sys.path.insert(0, os.path.join(ref_root, "src"))
@@ -86,7 +87,22 @@ def main():
         out[name + "/o"] = to_np(o)
         out[name + "/lse"] = lse.numpy()
     np.savez_compressed(os.path.join(HERE, "decode.npz"), **out)
-    for f in ("config1", "fwd", "bwd", "decode"):
+    # ---- RoPE: reference forward, and backward by autograd through its torch frontend ---------------
+    from stackkernels._reference.torch.rope import apply_rope as ref_rope, precompute_freqs as ref_freqs
+    from stackkernels.torch.embedding import apply_rope as ref_rope_autograd
+    out = {}
+    for name, c in ROPE_CASES.items():
+        x, dy, cos, sin = make_rope_inputs(c)
+        rc, rs = ref_freqs(c["D"], max_seq_len=cos.shape[0], dtype=cos.dtype)
+        assert torch.equal(rc, cos) and torch.equal(rs, sin)          # same tables as the reference builds
+        y = ref_rope(x, cos=cos, sin=sin, start_pos=c["start_pos"])
+        x1 = x.detach().clone().requires_grad_(True)
+        ref_rope_autograd(x1, cos=cos, sin=sin, start_pos=c["start_pos"]).backward(dy)
+        out[name + "/in_sum"] = input_checksum(x, dy, cos, sin)
+        out[name + "/y"] = to_np(y)
+        out[name + "/dx"] = to_np(x1.grad)
+    np.savez_compressed(os.path.join(HERE, "rope.npz"), **out)
+    for f in ("config1", "fwd", "bwd", "decode", "rope"):
         print(f, os.path.getsize(os.path.join(HERE, f + ".npz")), "bytes")
 
 

@@ -1,0 +1,103 @@
+"""RoPE with start_pos and the KV-cache append (the steps right before attention / decode).
+CPU part: the oracle against stored outputs of the unmodified reference.  GPU part (marked gpu): the CUDA
+kernels, through the C ABI, against those stored outputs and the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from _cases import ROPE_CASES, TOL, input_checksum, load_golden, make_rope_inputs
+from _parity import assert_parity
+from oracle import rope_oracle as ro
+
+
+@pytest.mark.parametrize("name", sorted(ROPE_CASES))
+def test_rope_oracle_matches_reference(name):
+    c = ROPE_CASES[name]
+    g = load_golden("rope")
+    x, dy, cos, sin = make_rope_inputs(c)
+    assert abs(input_checksum(x, dy, cos, sin) - float(g[name + "/in_sum"])) < 1e-6
+    oc, os_ = ro.precompute_freqs(c["D"], cos.shape[0], dtype=cos.dtype)
+    assert torch.equal(oc, cos) and torch.equal(os_, sin)
+    y = ro.rope_forward(x, cos, sin, c["start_pos"])
+    dx = ro.rope_backward(dy, cos, sin, c["start_pos"])
+    assert torch.equal(y.float(), torch.as_tensor(g[name + "/y"]))        # same fp32 ops in the same order
+    assert torch.equal(dx.float(), torch.as_tensor(g[name + "/dx"]))
+
+
+def test_kv_append_oracle_semantics():
+    kc, vc = torch.zeros(2, 1, 6, 4), torch.zeros(2, 1, 6, 4)
+    kn, vn = torch.ones(2, 1, 2, 4), 2 * torch.ones(2, 1, 2, 4)
+    k2, v2, lens = ro.kv_append(kc, vc, kn, vn, [3, 5])
+    assert k2[0, 0, 3:5].eq(1).all() and k2[0, 0, :3].eq(0).all() and k2[0, 0, 5].eq(0).all()
+    assert v2[1, 0, 5].eq(2).all() and lens.tolist() == [5, 6]            # second row of sequence 1 dropped
+
+
+def _gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import stackkernels_b200
+    from stackkernels_b200 import _lib
+    _lib.load()
+    return stackkernels_b200
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(ROPE_CASES))
+def test_rope_kernel_vs_reference(name):
+    skb = _gpu()
+    from stackkernels_b200.embedding import rope_launch
+    c = ROPE_CASES[name]
+    g = load_golden("rope")
+    x, dy, cos, sin = make_rope_inputs(c)
+    xd = x.cuda().requires_grad_(True)
+    y = skb.apply_rope(xd, cos=cos.cuda(), sin=sin.cuda(), start_pos=c["start_pos"])
+    y.backward(dy.cuda())
+    assert y.shape == x.shape and y.dtype == x.dtype
+    assert_parity(y, g[name + "/y"], c["dtype"], f"{name} y")
+    assert_parity(xd.grad, g[name + "/dx"], c["dtype"], f"{name} dx")
+    # fused layout change: (B,S,H,D) -> (B,H,S,D)
+    yt = rope_launch(x.cuda(), cos.cuda(), sin.cuda(), c["start_pos"], out_bhsd=True)
+    assert torch.equal(yt, y.detach().transpose(1, 2).contiguous())
+
+
+@pytest.mark.gpu
+def test_rope_gqa_and_module():
+    skb = _gpu()
+    torch.manual_seed(0)
+    q, k = torch.randn(2, 8, 16, 128), torch.randn(2, 8, 4, 128)
+    cos, sin = ro.precompute_freqs(128, 23 + 8 + 64)
+    qr, kr = skb.apply_rope(q.cuda(), k.cuda(), cos=cos.cuda(), sin=sin.cuda(), start_pos=23)
+    torch.testing.assert_close(qr.cpu(), ro.rope_forward(q, cos, sin, 23), atol=1e-4, rtol=1e-4)
+    torch.testing.assert_close(kr.cpu(), ro.rope_forward(k, cos, sin, 23), atol=1e-4, rtol=1e-4)
+    m = skb.RoPE(dim=64, max_seq_len=512).cuda()
+    out = m(torch.randn(1, 10, 2, 64, device="cuda"), start_pos=500)
+    assert out.shape == (1, 10, 2, 64) and not torch.isnan(out).any()
+    with pytest.raises(ValueError):
+        m(torch.randn(1, 20, 2, 64, device="cuda"), start_pos=500)        # runs past the table
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_kv_append_then_decode(dtype):
+    skb = _gpu()
+    from oracle import attention_oracle as orc
+    torch.manual_seed(3)
+    B, Hq, Hkv, cap, D, T = 3, 8, 2, 300, 128, 2
+    kc, vc = torch.randn(B, Hkv, cap, D).to(dtype), torch.randn(B, Hkv, cap, D).to(dtype)
+    kn, vn = torch.randn(B, Hkv, T, D).to(dtype), torch.randn(B, Hkv, T, D).to(dtype)
+    lens = torch.tensor([0, 137, 299], dtype=torch.int32)
+    ek, ev, elens = ro.kv_append(kc, vc, kn, vn, lens)
+    kd, vd, ld = kc.cuda(), vc.cuda(), lens.cuda()
+    out_lens = skb.kv_cache_append(kd, vd, kn.cuda(), vn.cuda(), cache_seqlens=ld)
+    torch.cuda.synchronize()
+    assert torch.equal(kd.cpu(), ek) and torch.equal(vd.cpu(), ev)          # bit-exact copy, overflow row dropped
+    assert out_lens.cpu().tolist() == elens.tolist() == [2, 139, 300]
+    # the appended rows are what decode now attends to
+    q = torch.randn(B, Hq, 1, D).to(dtype)
+    o = skb.flash_decode(q.cuda(), kd, vd, cache_seqlens=ld)
+    eo, _ = orc.decode_forward(q, ek, ev, elens)
+    assert_parity(o, eo, "bf16" if dtype == torch.bfloat16 else "fp32", "decode after append")
+    # fixed start position form
+    k2, v2 = kc.cuda(), vc.cuda()
+    skb.kv_cache_append(k2, v2, kn.cuda(), vn.cuda(), start_pos=10)
+    assert torch.equal(k2[:, :, 10:12].cpu(), kn) and torch.equal(k2[:, :, :10].cpu(), kc[:, :, :10])
