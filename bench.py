@@ -304,7 +304,7 @@ def run_native(args):
         line["e2e"] = {"value": world * r["units"] * scale / r["e2e"]["s_step"], "unit": unit,
                        "h2d_bytes_per_step": r["e2e"]["h2d"], "d2h_bytes_per_step": r["e2e"]["d2h"]}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(name, budget_s=args.cpu_seconds)
+        line["cpu_baseline"] = cpu_baseline(name, limit_s=args.cpu_seconds)
     if world == 1 and not args.no_extras:
         extras = {}
         for en, st in (("prefill_fwd_s8192", 5), ("fwdbwd_c3", 2), ("decode_c4", 10), ("decode_c5", 10), ("rope_c3", 10)):
@@ -325,7 +325,7 @@ def run_native(args):
         dist.destroy_process_group()
 
 
-def cpu_baseline(name, budget_s=15.0):
+def cpu_baseline(name, limit_s=15.0):
     """The CPU restatement of the reference's CPU path, timed on a bounded sample of the workload."""
     from oracle import attention_oracle as orc
     kind, p = WORKLOADS[name]
@@ -337,7 +337,7 @@ def cpu_baseline(name, budget_s=15.0):
         g = p["Hq"] // p["Hkv"]
         S, D = p["S"], p["D"]
         per_slice = (2.0 if kind == "fwd" else 5.0) * g * S * S * D
-        while t_used < budget_s and n < p["B"] * p["Hkv"]:
+        while t_used < limit_s and n < p["B"] * p["Hkv"]:
             q = torch.randn(1, g, S, D).to(dt)
             k, v = torch.randn(1, 1, S, D).to(dt), torch.randn(1, 1, S, D).to(dt)
             t0 = time.perf_counter()
@@ -353,7 +353,7 @@ def cpu_baseline(name, budget_s=15.0):
     else:
         es = 2 if p["dtype"] != "fp32" else 4
         ln = p["cap"] if p["lens"] == "full" else (16384 + p["cap"]) // 2
-        while t_used < budget_s and n < p["B"]:
+        while t_used < limit_s and n < p["B"]:
             q = torch.randn(1, p["Hq"], 1, p["D"]).to(dt)
             k, v = torch.randn(1, p["Hkv"], ln, p["D"]).to(dt), torch.randn(1, p["Hkv"], ln, p["D"]).to(dt)
             t0 = time.perf_counter()
@@ -376,10 +376,10 @@ def run_reference(args):
     kind, p = WORKLOADS[name]
     per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
     for _ in range(args.warmup):
-        cpu_baseline(name, budget_s=per_step / 4)
+        cpu_baseline(name, limit_s=per_step / 4)
     vals, secs = [], 0.0
     for _ in range(args.steps):
-        r = cpu_baseline(name, budget_s=per_step)
+        r = cpu_baseline(name, limit_s=per_step)
         vals.append(r["value"])
         secs += r["seconds"]
     v = statistics.mean(vals)
@@ -392,7 +392,7 @@ def run_reference(args):
         "vs_baseline": None, "dtype": p["dtype"], "data": "synthetic",
         "config": {"workload": name, **{k: vv for k, vv in p.items() if k != "seed"}, "causal": not is_decode},
         "cpu_baseline": {"value": v, "unit": r["unit"], "cores": r["cores"], "kind": "port",
-                         "sample": r["sample"] + f" per step ({per_step:.0f} s budget)"},
+                         "sample": r["sample"] + f" per step ({per_step:.0f} s per step)"},
         "e2e": {"value": v, "unit": r["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }

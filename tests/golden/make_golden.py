@@ -1,6 +1,6 @@
 """Generate golden vectors from the UNMODIFIED reference (run in the build container only).
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [/path/to/reference]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference/checkout
 
 Imports ``stackkernels`` from the reference checkout, runs its CPU path
 (``attention_reference`` / ``flash_attention`` / ``flash_decode`` and autograd
@@ -22,7 +22,9 @@ from _cases import (FWD_CASES, BWD_CASES, DECODE_CASES, make_fwd_inputs, make_bw
                     make_decode_inputs, config1_inputs, input_checksum, to_np, ROWSTEP,
                     ROPE_CASES, make_rope_inputs)
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/reference/checkout")
+ref_root = sys.argv[1]
 sys.path.insert(0, os.path.join(ref_root, "src"))
 os.environ.setdefault("STACKKERNELS_BACKEND", "reference")
 from stackkernels._reference.torch.attention import attention_reference  # noqa: E402
