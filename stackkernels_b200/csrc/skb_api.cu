@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "decode_group.cuh"
+#include "decode_tc.cuh"
 #include "bwd_sm100.cuh"
 #include "fwd2_sm100.cuh"
 #include "aux_kernels.cuh"
@@ -292,6 +293,21 @@ int decode_group(const void* q, const void* kc, const void* vc, const int32_t* l
   if (int rc = make_map_3d(&mv, dt, vc, D, Scap, (size_t)B * Hkv, dgrp::kTileN)) return rc;
   const int G = Hq / Hkv;
   int rc;
+  if (D == 128 && G > 16) {
+    // wide groups: tcgen05 kernel with the group's heads as the MMA M dimension (decode_tc.cuh)
+    CUtensorMap mq, mk128, mv128;
+    if (int r2 = make_map_3d(&mq, dt, q, D, B * Hq, 1)) return r2;
+    if (int r2 = make_map_3d(&mk128, dt, kc, D, Scap, (size_t)B * Hkv)) return r2;
+    if (int r2 = make_map_3d(&mv128, dt, vc, D, Scap, (size_t)B * Hkv)) return r2;
+    auto kern = dtc::decode_kernel<T>;
+    if (int r2 = set_smem(kern, dtc::kSmemBytes)) return r2;
+    kern<<<dim3(nsplit, Hkv, B), dtc::kThreads, dtc::kSmemBytes, st>>>(mq, mk128, mv128, lens, part_o, part_ml, Hq, Hkv,
+                                                                      Scap, nsplit, scale * kLog2e);
+    SKB_CUDA(cudaGetLastError());
+    general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, lse, D, nsplit);
+    SKB_CUDA(cudaGetLastError());
+    return SKB_OK;
+  }
 #define SKB_DG(HD_, MT_) launch_decode_group<T, HD_, MT_>(mk, mv, q, lens, part_o, part_ml, B, Hq, Hkv, Scap, nsplit, scale, st)
   if (D == 64) rc = G <= 16 ? SKB_DG(64, 1) : (G <= 32 ? SKB_DG(64, 2) : SKB_DG(64, 4));
   else rc = G <= 16 ? SKB_DG(128, 1) : (G <= 32 ? SKB_DG(128, 2) : SKB_DG(128, 4));
