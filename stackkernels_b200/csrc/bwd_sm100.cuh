@@ -131,9 +131,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
            const float* __restrict__ lse2, const float* __restrict__ delta, float* __restrict__ dq_acc,
-           T* __restrict__ dk, T* __restrict__ dv, int Hq, int Hkv, int Sq, int Sk, int Sq_pad, int causal,
+           T* __restrict__ dk, T* __restrict__ dv, int Hq, int Hkv, int Sq, int Sk, int Sq_pad, int D, int causal,
            float scale, float scale_log2) {
-  constexpr int HD = 128;
+  // The tiles are 128 columns wide; D <= 128 (a multiple of 8) is the head dimension in memory.  The tensor
+  // maps cover D columns, so the bulk copies zero columns [D, 128) of Q, K, V and dO, which leaves every
+  // product unchanged; the dQ accumulator and the dK/dV rows are D wide and only those columns are written.
   constexpr uint32_t IDESC_S = ptx::idesc_f16(Fmt<T>::v, 128, kBwdQ, 0, 0);    // (a),(b): A K-major, B K-major, N = 64
   constexpr uint32_t IDESC_KM = ptx::idesc_f16(Fmt<T>::v, 128, 128, 0, 1);     // (c),(d): A K-major, B MN-major
   constexpr uint32_t IDESC_DQ = ptx::idesc_f16(Fmt<T>::v, 128, kBwdQ, 1, 1);   // (e): A MN-major, B MN-major, N = 64
@@ -421,13 +423,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         ptx::tmem_wait_ld();
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar(B_RP_FREE + w));
-        float* dst = dq_acc + ((size_t)(b * Hq + head_of(u)) * Sq + q0) * HD + r;
+        float* dst = dq_acc + ((size_t)(b * Hq + head_of(u)) * Sq + q0) * D + r;
+        const int q_lim = r < D ? Sq - q0 : 0;       // lanes past the head dimension hold zeros: nothing to add
 #pragma unroll
         for (int c = 0; c < 32; ++c)
-          if (q0 + c < Sq) red_add(dst + (size_t)c * HD, __uint_as_float(qa[c]));
+          if (c < q_lim) red_add(dst + (size_t)c * D, __uint_as_float(qa[c]));
 #pragma unroll
         for (int c = 0; c < 32; ++c)
-          if (q0 + 32 + c < Sq) red_add(dst + (size_t)(32 + c) * HD, __uint_as_float(qb[c]));
+          if (32 + c < q_lim) red_add(dst + (size_t)(32 + c) * D, __uint_as_float(qb[c]));
       }
       if (wq == 0 && lane == 0) SKB_TR(1 + w, u >> 1, 5);
     }
@@ -442,7 +445,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const size_t row = ((size_t)b * Hkv + hkv) * Sk + min(kvidx, Sk - 1);
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        T* dst = (which == 0 ? dk : dv) + row * HD + 64 * w;
+        T* dst = (which == 0 ? dk : dv) + row * D + 64 * w;
         const float mul = which == 0 ? scale : 1.f;
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2) {
@@ -457,6 +460,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           if (kvidx < Sk) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
+              if (64 * w + 32 * c2 + i >= D) break;
               uint4 o4;
               o4.x = pack2(__uint_as_float(ar[i]) * mul, __uint_as_float(ar[i + 1]) * mul, T());
               o4.y = pack2(__uint_as_float(ar[i + 2]) * mul, __uint_as_float(ar[i + 3]) * mul, T());

@@ -65,7 +65,9 @@ template <typename T, int HD, int MT>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const T* __restrict__ q, const int32_t* __restrict__ seqlens, float* __restrict__ part_o,
-              float2* __restrict__ part_ml, int Hq, int Hkv, int Scap, int nsplit, float scale_log2) {
+              float2* __restrict__ part_ml, int Hq, int Hkv, int Scap, int D, int nsplit, float scale_log2) {
+  // D <= HD (a multiple of 8) is the head dimension in memory: the tensor maps cover D columns, so the bulk
+  // copies zero columns [D, HD) of the K/V tiles; Q is read and the partial O written D columns wide.
   constexpr int TILE = tile_bytes<HD>();
   constexpr int NP = kComputeWarps / MT;      // warps sharing one M tile split the tile's rows NP ways
   constexpr int NW = kTileN / NP;             // tile rows per warp
@@ -134,14 +136,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   uint32_t qf[KS][4];
   {
-    const T* qb = q + ((size_t)b * Hq + (size_t)hkv * G) * HD;
+    const T* qb = q + ((size_t)b * Hq + (size_t)hkv * G) * D;
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
       const int c = 16 * kk + 2 * tq;
-      qf[kk][0] = r_lo < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * HD + c) : 0u;
-      qf[kk][1] = r_hi < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * HD + c) : 0u;
-      qf[kk][2] = r_lo < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * HD + c + 8) : 0u;
-      qf[kk][3] = r_hi < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * HD + c + 8) : 0u;
+      const bool lo = r_lo < G, hi = r_hi < G, c0 = c < D, c1 = c + 8 < D;
+      qf[kk][0] = lo && c0 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * D + c) : 0u;
+      qf[kk][1] = hi && c0 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * D + c) : 0u;
+      qf[kk][2] = lo && c1 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * D + c + 8) : 0u;
+      qf[kk][3] = hi && c1 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * D + c + 8) : 0u;
     }
   }
   float oacc[NT_O][4];
@@ -266,7 +269,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   const int tid = threadIdx.x;   // 0..127
   for (int idx = tid; idx < MT * 16 * (HD / 4); idx += kComputeWarps * 32) {
     const int hrow = idx / (HD / 4), c4 = (idx % (HD / 4)) * 4;
-    if (hrow >= G) continue;
+    if (hrow >= G || c4 >= D) continue;
     const int tmt = hrow >> 4, r = hrow & 15;
     float M = -INFINITY;
 #pragma unroll
@@ -284,7 +287,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       }
     }
     const size_t pbase = ((size_t)b * Hq + (size_t)hkv * G + hrow) * nsplit + split;
-    *reinterpret_cast<float4*>(part_o + pbase * HD + c4) = acc;
+    *reinterpret_cast<float4*>(part_o + pbase * D + c4) = acc;
     if (c4 == 0) part_ml[pbase] = make_float2(M, L);
   }
 }

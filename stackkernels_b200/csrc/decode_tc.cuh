@@ -42,9 +42,9 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const int32_t* __restrict__ seqlens,
-              float* __restrict__ part_o, float2* __restrict__ part_ml, int Hq, int Hkv, int Scap, int nsplit,
+              float* __restrict__ part_o, float2* __restrict__ part_ml, int Hq, int Hkv, int Scap, int D, int nsplit,
               float scale_log2) {
-  constexpr int HD = 128;
+  // D <= 128 (a multiple of 8) is the head dimension in memory; the bulk copies zero columns [D, 128).
   constexpr uint32_t IDESC_QK = ptx::idesc_f16(Fmt<T>::v, 128, 128, 0, 0);
   constexpr uint32_t IDESC_PV = ptx::idesc_f16(Fmt<T>::v, 128, 128, 0, 1);
 
@@ -272,7 +272,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (r < G) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<uint4*>(part_o + pbase * HD + c * 32 + i) =
+            if (c * 32 + i < D)
+              *reinterpret_cast<uint4*>(part_o + pbase * D + c * 32 + i) =
                 seen ? make_uint4(orr[i], orr[i + 1], orr[i + 2], orr[i + 3]) : make_uint4(0u, 0u, 0u, 0u);
         }
       }

@@ -77,7 +77,10 @@ template <typename T, int HD>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, T* __restrict__ o, float* __restrict__ lse,
-           int Hq, int Hkv, int Sq, int Sk, int causal, float scale_log2) {
+           int Hq, int Hkv, int Sq, int Sk, int D, int causal, float scale_log2) {
+  // D <= HD is the head dimension in memory (a multiple of 8): the tensor maps are built over D columns, so
+  // the bulk copies fill columns [D, HD) of every Q/K/V tile with zeros and the products are unchanged; only
+  // the first D columns of O are stored.
   constexpr int TILE = fwd_tile_bytes<HD>();
   constexpr int KSTEPS_QK = HD / 16;
   constexpr int KSTEPS_PV = kTileN / 16;
@@ -337,7 +340,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ptx::tc_fence_after();
       const bool seen = (m != -INFINITY) && l > 0.f;    // false: no visible key in the whole row
       const float inv = seen ? 1.f / l : 0.f;
-      T* orow = o + ((size_t)bhq * Sq + (size_t)min(grow, Sq - 1)) * HD;
+      T* orow = o + ((size_t)bhq * Sq + (size_t)min(grow, Sq - 1)) * D;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t orr[32];
@@ -351,6 +354,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (grow < Sq) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
+            if (c * 32 + i >= D) break;
             uint4 w;
             w.x = pack2(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv, T());
             w.y = pack2(__uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv, T());

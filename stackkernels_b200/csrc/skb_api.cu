@@ -178,22 +178,24 @@ int make_map_3d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, size
 }
 
 bool fwd_sm100_covers(int D, int dtype, float scale) {
-  return (dtype == SKB_F16 || dtype == SKB_BF16) && (D == 64 || D == 128) && scale > 0.f;
+  // any D <= 128 (a multiple of 8): the kernels are built for 64 and 128 columns and D is zero-padded
+  // up to the next of the two by the bulk copies
+  return (dtype == SKB_F16 || dtype == SKB_BF16) && D <= 128 && D % 8 == 0 && scale > 0.f;
 }
 
 template <typename T, int HD>
 int launch_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
-                     int Sk, int causal, float scale, cudaStream_t st) {
+                     int Sk, int D, int causal, float scale, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   const int dt = DtypeOf<T>::value;
-  if (int rc = make_map_3d(&mq, dt, q, HD, Sq, (size_t)B * Hq)) return rc;
-  if (int rc = make_map_3d(&mk, dt, k, HD, Sk, (size_t)B * Hkv)) return rc;
-  if (int rc = make_map_3d(&mv, dt, v, HD, Sk, (size_t)B * Hkv)) return rc;
+  if (int rc = make_map_3d(&mq, dt, q, D, Sq, (size_t)B * Hq)) return rc;
+  if (int rc = make_map_3d(&mk, dt, k, D, Sk, (size_t)B * Hkv)) return rc;
+  if (int rc = make_map_3d(&mv, dt, v, D, Sk, (size_t)B * Hkv)) return rc;
   auto kern = sm100::fwd_kernel<T, HD>;
   constexpr size_t smem = sm100::fwd_smem_bytes<HD>();
   if (int rc = set_smem(kern, smem)) return rc;
   dim3 grid(cdiv(Sq, 2 * sm100::kTileM), Hq, B);
-  kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, lse, Hq, Hkv, Sq, Sk, causal, scale * kLog2e);
+  kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, lse, Hq, Hkv, Sq, Sk, D, causal, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -217,7 +219,8 @@ int launch_fwd2_sm100(const void* q, const void* k, const void* v, void* o, floa
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // ------------------------------------------------------------------------------------ tensor-core backward
-bool bwd_sm100_covers(int D, int dtype) { return (dtype == SKB_F16 || dtype == SKB_BF16) && D == 128; }
+// any D <= 128 (a multiple of 8) runs on the 128-column kernel with zero padding by the bulk copies
+bool bwd_sm100_covers(int D, int dtype) { return (dtype == SKB_F16 || dtype == SKB_BF16) && D <= 128 && D % 8 == 0; }
 
 struct BwdWs {           // carve-up of the backward workspace for the tensor-core path
   size_t delta_off, lse2_off, dq_off, total;
@@ -235,9 +238,8 @@ BwdWs bwd_sm100_ws(int B, int Hq, int Sq, int D) {
 
 template <typename T>
 int launch_bwd_sm100(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
-                     void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk, int causal, float scale,
+                     void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk, int D, int causal, float scale,
                      void* workspace, cudaStream_t st) {
-  constexpr int D = 128;
   const BwdWs w = bwd_sm100_ws(B, Hq, Sq, D);
   float* delta = (float*)((char*)workspace + w.delta_off);
   float* lse2 = (float*)((char*)workspace + w.lse2_off);
@@ -259,7 +261,7 @@ int launch_bwd_sm100(const void* dout, const void* q, const void* k, const void*
   auto kern = sm100::bwd_kernel<T>;
   if (int rc = set_smem(kern, sm100::kBwdSmemBytes)) return rc;
   kern<<<dim3(cdiv(Sk, 128), Hkv, B), sm100::kBwdThreads, sm100::kBwdSmemBytes, st>>>(
-      mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)dk, (T*)dv, Hq, Hkv, Sq, Sk, sq_pad, causal, scale, scale * kLog2e);
+      mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)dk, (T*)dv, Hq, Hkv, Sq, Sk, sq_pad, D, causal, scale, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   const size_t n4 = bh * Sq * D / 4;
   sm100::bwd_post_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_acc, (T*)dq, scale, n4);
@@ -269,17 +271,21 @@ int launch_bwd_sm100(const void* dout, const void* q, const void* k, const void*
 
 // ------------------------------------------------------------------------------------ group decode
 bool decode_group_covers(int Hq, int Hkv, int D, int dtype) {
-  return (dtype == SKB_F16 || dtype == SKB_BF16) && (D == 64 || D == 128) && Hq / Hkv <= 64;
+  return (dtype == SKB_F16 || dtype == SKB_BF16) && D <= 128 && D % 8 == 0 && Hq / Hkv <= 64;
 }
+// Within the group path: more than 16 query heads per KV head at 64 < D <= 128 run on tcgen05
+// (decode_tc.cuh), narrower groups and D <= 64 on the mma.sync kernel (decode_group.cuh).  Both kernels
+// are built for 64- or 128-column tiles; other D are zero-padded by the bulk copies.
+bool decode_uses_tcgen05(int Hq, int Hkv, int D) { return D > 64 && D <= 128 && Hq / Hkv > 16; }
 
 template <typename T, int HD, int MT>
 int launch_decode_group(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int32_t* lens, float* part_o,
-                        float2* part_ml, int B, int Hq, int Hkv, int Scap, int nsplit, float scale, cudaStream_t st) {
+                        float2* part_ml, int B, int Hq, int Hkv, int Scap, int D, int nsplit, float scale, cudaStream_t st) {
   auto kern = dgrp::decode_kernel<T, HD, MT>;
   constexpr size_t smem = dgrp::smem_bytes<HD>();
   if (int rc = set_smem(kern, smem)) return rc;
   kern<<<dim3(nsplit, Hkv, B), dgrp::kThreads, smem, st>>>(mk, mv, (const T*)q, lens, part_o, part_ml, Hq, Hkv, Scap,
-                                                          nsplit, scale * kLog2e);
+                                                          D, nsplit, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -287,13 +293,10 @@ int launch_decode_group(const CUtensorMap& mk, const CUtensorMap& mv, const void
 template <typename T>
 int decode_group(const void* q, const void* kc, const void* vc, const int32_t* lens, void* o, float* lse, int B, int Hq,
                  int Hkv, int Scap, int D, int nsplit, float scale, float* part_o, float2* part_ml, cudaStream_t st) {
-  CUtensorMap mk, mv;
   const int dt = DtypeOf<T>::value;
-  if (int rc = make_map_3d(&mk, dt, kc, D, Scap, (size_t)B * Hkv, dgrp::kTileN)) return rc;
-  if (int rc = make_map_3d(&mv, dt, vc, D, Scap, (size_t)B * Hkv, dgrp::kTileN)) return rc;
   const int G = Hq / Hkv;
   int rc;
-  if (D == 128 && G > 16) {
+  if (decode_uses_tcgen05(Hq, Hkv, D)) {
     // wide groups: tcgen05 kernel with the group's heads as the MMA M dimension (decode_tc.cuh)
     CUtensorMap mq, mk128, mv128;
     if (int r2 = make_map_3d(&mq, dt, q, D, B * Hq, 1)) return r2;
@@ -302,14 +305,17 @@ int decode_group(const void* q, const void* kc, const void* vc, const int32_t* l
     auto kern = dtc::decode_kernel<T>;
     if (int r2 = set_smem(kern, dtc::kSmemBytes)) return r2;
     kern<<<dim3(nsplit, Hkv, B), dtc::kThreads, dtc::kSmemBytes, st>>>(mq, mk128, mv128, lens, part_o, part_ml, Hq, Hkv,
-                                                                      Scap, nsplit, scale * kLog2e);
+                                                                      Scap, D, nsplit, scale * kLog2e);
     SKB_CUDA(cudaGetLastError());
     general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, lse, D, nsplit);
     SKB_CUDA(cudaGetLastError());
     return SKB_OK;
   }
-#define SKB_DG(HD_, MT_) launch_decode_group<T, HD_, MT_>(mk, mv, q, lens, part_o, part_ml, B, Hq, Hkv, Scap, nsplit, scale, st)
-  if (D == 64) rc = G <= 16 ? SKB_DG(64, 1) : (G <= 32 ? SKB_DG(64, 2) : SKB_DG(64, 4));
+  CUtensorMap mk, mv;
+  if (int r2 = make_map_3d(&mk, dt, kc, D, Scap, (size_t)B * Hkv, dgrp::kTileN)) return r2;
+  if (int r2 = make_map_3d(&mv, dt, vc, D, Scap, (size_t)B * Hkv, dgrp::kTileN)) return r2;
+#define SKB_DG(HD_, MT_) launch_decode_group<T, HD_, MT_>(mk, mv, q, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st)
+  if (D <= 64) rc = G <= 16 ? SKB_DG(64, 1) : (G <= 32 ? SKB_DG(64, 2) : SKB_DG(64, 4));
   else rc = G <= 16 ? SKB_DG(128, 1) : (G <= 32 ? SKB_DG(128, 2) : SKB_DG(128, 4));
 #undef SKB_DG
   if (rc) return rc;
@@ -392,10 +398,10 @@ int skb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
   }
   if (use_tc) {
     if (dtype == SKB_F16)
-      return D == 64 ? launch_fwd_sm100<__half, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st)
-                     : launch_fwd_sm100<__half, 128>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
-    return D == 64 ? launch_fwd_sm100<__nv_bfloat16, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st)
-                   : launch_fwd_sm100<__nv_bfloat16, 128>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
+      return D <= 64 ? launch_fwd_sm100<__half, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st)
+                     : launch_fwd_sm100<__half, 128>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+    return D <= 64 ? launch_fwd_sm100<__nv_bfloat16, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st)
+                   : launch_fwd_sm100<__nv_bfloat16, 128>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
   }
   switch (dtype) {
     case SKB_F32: return fwd_general<float>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
@@ -431,8 +437,8 @@ int skb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, 
   cudaStream_t st = (cudaStream_t)stream;
   if (impl == SKB_IMPL_SM100 || (impl == SKB_IMPL_AUTO && covers && Sq >= 128 && Sk >= 128)) {
     if (dtype == SKB_F16)
-      return launch_bwd_sm100<__half>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, causal, scale, workspace, st);
-    return launch_bwd_sm100<__nv_bfloat16>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, causal, scale, workspace, st);
+      return launch_bwd_sm100<__half>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, workspace, st);
+    return launch_bwd_sm100<__nv_bfloat16>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, workspace, st);
   }
   float* delta = (float*)workspace;
   switch (dtype) {
@@ -448,6 +454,17 @@ int skb_decode_num_splits(int B, int Hq, int Hkv, int Scap, int D, int dtype, in
   if (Scap <= 128) return 1;
   // one CTA per (split, kv head) when the group kernel applies, per (split, q head) otherwise
   const long long units = (long long)B * (decode_group_covers(Hq, Hkv, D, dtype) ? Hkv : Hq);
+  if (decode_group_covers(Hq, Hkv, D, dtype) && decode_uses_tcgen05(Hq, Hkv, D)) {
+    // The tcgen05 kernel runs one CTA per SM, so nothing hides a CTA's start-up and drain (about 3 us):
+    // one wave of CTAs, or two when each SM has more than ~64 tiles of 128 rows to stream, so that ragged
+    // lengths still even out.
+    const long long tiles_per_sm = units * ((Scap + 127) / 128) / sm_count;
+    long long s = (tiles_per_sm >= 64 ? 2LL : 1LL) * sm_count / units;
+    const long long cap = Scap / 256;
+    if (s > cap) s = cap;
+    if (s > 128) s = 128;
+    return (int)(s < 1 ? 1 : s);
+  }
   long long by_fill = (4LL * sm_count + units - 1) / units;   // enough CTAs to fill the GPU a few times over
   long long by_len = Scap / 2048;                              // ~2K rows per split balances ragged lengths
   long long s = by_fill > by_len ? by_fill : by_len;

@@ -6,12 +6,14 @@ nearly equal reals can differ by one unit in the last place, which exceeds the a
 once |x| > 2.56 (bf16) / 10.2 (fp16).  For such elements the allowance is one ulp
 (2^-7 |x| for bf16, 2^-10 |x| for fp16); everywhere else the absolute bar applies unchanged.
 
-dK / dV of a GQA/MQA group in 16 bits are a special case of the same effect: the reference's CPU
-path (autograd through ``repeat_interleave`` of a 16-bit tensor) rounds each query head's
-contribution to 16 bits and adds the G contributions in 16 bits, while the CUDA kernels -- like
-the reference's own GPU kernel -- accumulate the group in fp32 and round once.  Against the stored
-reference outputs those tensors get ``ulps=G``; against the oracle, which also rounds once, they
-get the normal one-ulp allowance.
+dK / dV of a GQA/MQA group in 16 bits are a special case: the reference's CPU path (autograd through
+``repeat_interleave`` of a 16-bit tensor) rounds each query head's contribution to 16 bits and adds
+the G contributions in 16 bits, while the CUDA kernels -- like the reference's own GPU kernel --
+accumulate the group in fp32 and round once.  The stored reference outputs therefore sit up to a few
+16-bit ulps *of the largest contribution* away from the exact sum (0.016 on dK, 0.031 on dV in the
+committed cases, measured against the fp32 oracle), more than the bar where contributions cancel.
+Against the stored outputs those tensors are given ``slack`` = the stored value's own distance from
+the oracle, element by element; against the oracle, which also rounds once, the bar applies as is.
 """
 import numpy as np
 import torch
@@ -30,7 +32,7 @@ def max_abs_err(ours, ref):
     return (a[fin] - b[fin]).abs().max().item()
 
 
-def assert_parity(ours, ref, dtype, what="", ulps=1):
+def assert_parity(ours, ref, dtype, what="", ulps=1, slack=None):
     a = ours.detach().float().cpu()
     b = torch.as_tensor(np.asarray(ref)).float() if not torch.is_tensor(ref) else ref.detach().float().cpu()
     assert a.shape == b.shape, f"{what}: shape {tuple(a.shape)} vs {tuple(b.shape)}"
@@ -40,5 +42,7 @@ def assert_parity(ours, ref, dtype, what="", ulps=1):
     if fin.any():
         err = (a[fin] - b[fin]).abs()
         allowed = torch.clamp(b[fin].abs() * (_ULP_REL[dtype] * ulps), min=TOL[dtype])
+        if slack is not None:
+            allowed = allowed + torch.as_tensor(np.asarray(slack)).float()[fin]
         worst = (err - allowed).max().item()
         assert worst <= 0, f"{what}: max abs err {err.max().item():.3e} (bar {TOL[dtype]:.0e}, dtype {dtype})"

@@ -76,13 +76,16 @@ def test_backward_vs_reference_autograd(skb, name):
     torch.cuda.synchronize()
     assert_parity(o[:, :, ::ROWSTEP], g[name + "/o"], c["dtype"], f"{name} O")
     assert_parity(q.grad[:, :, ::ROWSTEP], g[name + "/dq"], c["dtype"], f"{name} dQ")
-    G = c["Hq"] // c["Hkv"]
-    assert_parity(k.grad[:, :, ::ROWSTEP], g[name + "/dk"], c["dtype"], f"{name} dK", ulps=G)
-    assert_parity(v.grad[:, :, ::ROWSTEP], g[name + "/dv"], c["dtype"], f"{name} dV", ulps=G)
-    # and against the oracle, which like the kernels sums the group in fp32 and rounds once
+    # the oracle sums a GQA group in fp32 and rounds once, like the kernels; the stored reference outputs
+    # carry the 16-bit group sum of the reference's CPU autograd, whose distance from the oracle is the slack
     from oracle import attention_oracle as orc
     qc, kc, vc, doc = make_bwd_inputs(c)
     edq, edk, edv = orc.attention_backward(doc, qc, kc, vc, causal=c["causal"], scale=c["scale"])
+    gdk, gdv = torch.as_tensor(g[name + "/dk"]).float(), torch.as_tensor(g[name + "/dv"]).float()
+    assert_parity(k.grad[:, :, ::ROWSTEP], gdk, c["dtype"], f"{name} dK",
+                  slack=(gdk - edk[:, :, ::ROWSTEP].float()).abs())
+    assert_parity(v.grad[:, :, ::ROWSTEP], gdv, c["dtype"], f"{name} dV",
+                  slack=(gdv - edv[:, :, ::ROWSTEP].float()).abs())
     assert_parity(q.grad, edq, c["dtype"], f"{name} dQ vs oracle")
     assert_parity(k.grad, edk, c["dtype"], f"{name} dK vs oracle")
     assert_parity(v.grad, edv, c["dtype"], f"{name} dV vs oracle")
@@ -98,7 +101,7 @@ def test_decode_vs_reference(skb, name):
     lens_d = None if lens is None else lens.cuda()
     from stackkernels_b200.launchers import flash_decode as core
     impls = ["general"]
-    if c["dtype"] in ("fp16", "bf16") and c["D"] in (64, 128) and c["Hq"] // c["Hkv"] <= 64:
+    if c["dtype"] in ("fp16", "bf16") and c["D"] <= 128 and c["Hq"] // c["Hkv"] <= 64:
         impls.append("sm100")          # the group-per-CTA tensor-core kernel
     for impl in impls:
         for splits in (0, 1, 3):
@@ -115,7 +118,43 @@ def test_decode_vs_reference(skb, name):
     assert_parity(o_pub, g[name + "/o"], c["dtype"], f"{name} public")
 
 
-# shapes for the tensor-core backward (16-bit, D=128) checked against the oracle: ragged tails, S_q != S_k
+# decode with head dimensions that the group kernels zero-pad to their 64- or 128-column tiles, checked against
+# the oracle: narrow groups (mma.sync kernel) and wide groups (tcgen05 kernel), ragged and empty lengths
+PADDED_DECODE_CASES = {
+    "bf16_gqa4_d96": dict(B=3, Hq=8, Hkv=2, Scap=1500, D=96, dtype="bf16", seed=71, lens=[1500, 0, 333]),
+    "fp16_gqa8_d80": dict(B=2, Hq=16, Hkv=2, Scap=700, D=80, dtype="fp16", seed=72, lens=None),
+    "bf16_mha_d32": dict(B=2, Hq=4, Hkv=4, Scap=520, D=32, dtype="bf16", seed=73, lens=[129, 520]),
+    "fp16_mqa32_d96": dict(B=2, Hq=32, Hkv=1, Scap=2100, D=96, dtype="fp16", seed=74, lens=[2100, 1]),
+    "bf16_gqa64_d80": dict(B=2, Hq=128, Hkv=2, Scap=1024, D=80, dtype="bf16", seed=75, lens=[1000, 0]),
+    "bf16_gqa24_d128": dict(B=1, Hq=48, Hkv=2, Scap=3000, D=128, dtype="bf16", seed=76, lens=[2999]),
+}
+
+
+@pytest.mark.parametrize("name", sorted(PADDED_DECODE_CASES))
+def test_decode_padded_head_dim_vs_oracle(skb, name):
+    from _cases import DT
+    from oracle import attention_oracle as orc
+    from stackkernels_b200.launchers import flash_decode as core
+    c = PADDED_DECODE_CASES[name]
+    torch.manual_seed(c["seed"])
+    dt = DT[c["dtype"]]
+    q = torch.randn(c["B"], c["Hq"], 1, c["D"]).to(dt)
+    k = torch.randn(c["B"], c["Hkv"], c["Scap"], c["D"]).to(dt)
+    v = torch.randn(c["B"], c["Hkv"], c["Scap"], c["D"]).to(dt)
+    lens = None if c["lens"] is None else torch.tensor(c["lens"], dtype=torch.int32)
+    eo, el = orc.decode_forward(q, k, v, cache_seqlens=lens)
+    lens_d = None if lens is None else lens.cuda()
+    for impl in ("general", "sm100"):
+        for splits in (0, 1, 5):
+            o, lse = core(q.cuda(), k.cuda(), v.cuda(), cache_seqlens=lens_d, return_lse=True, num_splits=splits,
+                          impl=impl)
+            torch.cuda.synchronize()
+            assert_parity(o, eo, c["dtype"], f"{name}[{impl}, splits={splits}] O")
+            assert_parity(lse, el, c["dtype"], f"{name}[{impl}, splits={splits}] LSE")
+    _check_status()
+
+
+# shapes for the tensor-core forward/backward (16-bit) checked against the oracle: ragged tails, S_q != S_k, D < 128
 # in both directions (incl. fully masked query rows), MQA/GQA/MHA, causal and full
 TC_BWD_CASES = {
     "bf16_gqa_s300_causal": dict(B=1, Hq=4, Hkv=2, Sq=300, Sk=300, causal=True, dtype="bf16", seed=51),
@@ -124,6 +163,12 @@ TC_BWD_CASES = {
     "bf16_mha_s256x512_full": dict(B=2, Hq=2, Hkv=2, Sq=256, Sk=512, causal=False, dtype="bf16", seed=54),
     "fp16_gqa_s640_causal": dict(B=1, Hq=8, Hkv=2, Sq=640, Sk=640, causal=True, dtype="fp16", seed=55),
     "bf16_gqa_s128_causal": dict(B=2, Hq=4, Hkv=2, Sq=128, Sk=128, causal=True, dtype="bf16", seed=56),
+    # head dimensions below the 128-column tile: zero-padded by the bulk copies
+    "bf16_gqa_s300_d64_causal": dict(B=1, Hq=4, Hkv=2, Sq=300, Sk=300, D=64, causal=True, dtype="bf16", seed=57),
+    "fp16_mha_s200x260_d80_causal": dict(B=1, Hq=2, Hkv=2, Sq=200, Sk=260, D=80, causal=True, dtype="fp16", seed=58),
+    "bf16_gqa_s256_d96_full": dict(B=2, Hq=4, Hkv=1, Sq=256, Sk=256, D=96, causal=False, dtype="bf16", seed=59),
+    "bf16_mha_s130_d32_causal": dict(B=1, Hq=2, Hkv=2, Sq=130, Sk=130, D=32, causal=True, dtype="bf16", seed=60),
+    "fp16_gqa_s192_d120_causal": dict(B=1, Hq=4, Hkv=2, Sq=192, Sk=192, D=120, causal=True, dtype="fp16", seed=61),
 }
 
 
@@ -135,12 +180,18 @@ def test_tensor_core_backward_vs_oracle(skb, name):
     c = TC_BWD_CASES[name]
     torch.manual_seed(c["seed"])
     dt = DT[c["dtype"]]
-    q = torch.randn(c["B"], c["Hq"], c["Sq"], 128).to(dt)
-    k = torch.randn(c["B"], c["Hkv"], c["Sk"], 128).to(dt)
-    v = torch.randn(c["B"], c["Hkv"], c["Sk"], 128).to(dt)
-    do = torch.randn(c["B"], c["Hq"], c["Sq"], 128).to(dt)
+    D = c.get("D", 128)
+    q = torch.randn(c["B"], c["Hq"], c["Sq"], D).to(dt)
+    k = torch.randn(c["B"], c["Hkv"], c["Sk"], D).to(dt)
+    v = torch.randn(c["B"], c["Hkv"], c["Sk"], D).to(dt)
+    do = torch.randn(c["B"], c["Hq"], c["Sq"], D).to(dt)
     qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
-    o, lse = flash_attn_fwd(qd, kd, vd, is_causal=c["causal"])
+    eo, el = orc.attention_forward(q, k, v, causal=c["causal"])
+    for impl in ("general", "sm100"):
+        o, lse = flash_attn_fwd(qd, kd, vd, is_causal=c["causal"], impl=impl)
+        torch.cuda.synchronize()
+        assert_parity(o, eo, c["dtype"], f"{name}[{impl}] O")
+        assert_parity(lse, el, c["dtype"], f"{name}[{impl}] LSE")
     edq, edk, edv = orc.attention_backward(do, q, k, v, causal=c["causal"])
     for impl in ("general", "sm100"):
         dq, dk, dv = flash_attn_bwd(dod, qd, kd, vd, o, lse, is_causal=c["causal"], impl=impl)
