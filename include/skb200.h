@@ -94,6 +94,36 @@ int skb_decode(const void* q, const void* k_cache, const void* v_cache, const in
                int dtype, float scale, int num_splits, int impl,
                void* workspace, size_t workspace_bytes, void* stream);
 
+/* Strided variants of the three calls above, for tensors that are views of another layout -- typically
+ * (B,S,H,D) projections seen as (B,H,S,D) through transpose(1,2), which the reference copies with
+ * .contiguous() before every launch (src/stackkernels/torch/attention.py:38-40, 66;
+ * src/stackkernels/_core/attention/flash_fwd.py:206-208).  Every 4-D tensor comes with three int64 element
+ * strides {batch, head, sequence}; the head dimension itself must be contiguous.  Each stride of a dimension
+ * with more than one entry must be a positive multiple of 8 elements and each base pointer 16-byte
+ * aligned (SKB_ERR_ALIGN otherwise).  Outputs are written through their own strides; LSE stays
+ * (B,Hq,Sq) contiguous.  Only the tensor-core paths address strided tensors: when the shape, dtype or
+ * `impl` selects a general kernel and some tensor is not contiguous, SKB_ERR_UNSUPPORTED is returned and
+ * nothing runs (the caller then copies, as the reference does).  With contiguous strides these calls are
+ * the plain ones. */
+int skb_attn_fwd_strided(const void* q, const int64_t* q_strides, const void* k, const int64_t* k_strides,
+                         const void* v, const int64_t* v_strides, void* o, const int64_t* o_strides, float* lse,
+                         int B, int Hq, int Hkv, int Sq, int Sk, int D,
+                         int dtype, int causal, float scale, int impl, void* stream);
+int skb_attn_bwd_strided(const void* dout, const int64_t* dout_strides, const void* q, const int64_t* q_strides,
+                         const void* k, const int64_t* k_strides, const void* v, const int64_t* v_strides,
+                         const void* o, const int64_t* o_strides, const float* lse,
+                         void* dq, const int64_t* dq_strides, void* dk, const int64_t* dk_strides,
+                         void* dv, const int64_t* dv_strides,
+                         int B, int Hq, int Hkv, int Sq, int Sk, int D,
+                         int dtype, int causal, float scale, int impl,
+                         void* workspace, size_t workspace_bytes, void* stream);
+int skb_decode_strided(const void* q, const int64_t* q_strides, const void* k_cache, const int64_t* k_strides,
+                       const void* v_cache, const int64_t* v_strides, const int32_t* cache_seqlens,
+                       void* o, const int64_t* o_strides, float* lse,
+                       int B, int Hq, int Hkv, int Scap, int D,
+                       int dtype, float scale, int num_splits, int impl,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* Decode for callers that must not allocate device memory.
  *
  * Some hosts of this library run where an allocation is off the table: an inference server whose

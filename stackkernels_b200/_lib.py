@@ -22,6 +22,7 @@ IMPL_BY_NAME = {"auto": IMPL_AUTO, "general": IMPL_GENERAL, "sm100": IMPL_SM100,
 
 _c = ctypes
 _vp, _i, _f, _sz = _c.c_void_p, _c.c_int, _c.c_float, _c.c_size_t
+_sp = _c.POINTER(_c.c_int64)          # int64[3]: element strides of (batch, head, sequence)
 
 # name -> (restype, argtypes); every symbol include/skb200.h declares
 SIGNATURES = {
@@ -32,6 +33,9 @@ SIGNATURES = {
     "skb_decode_workspace_bytes": (_sz, [_i] * 7),
     "skb_decode": (_i, [_vp] * 6 + [_i] * 5 + [_i, _f, _i, _i, _vp, _sz, _vp]),
     "skb_decode_noalloc": (_i, [_vp] * 6 + [_i] * 5 + [_i, _f, _i, _vp]),
+    "skb_attn_fwd_strided": (_i, [_vp, _sp] * 4 + [_vp] + [_i] * 6 + [_i, _i, _f, _i, _vp]),
+    "skb_attn_bwd_strided": (_i, [_vp, _sp] * 5 + [_vp] + [_vp, _sp] * 3 + [_i] * 6 + [_i, _i, _f, _i, _vp, _sz, _vp]),
+    "skb_decode_strided": (_i, [_vp, _sp] * 3 + [_vp] + [_vp, _sp] + [_vp] + [_i] * 5 + [_i, _f, _i, _i, _vp, _sz, _vp]),
     "skb_rope": (_i, [_vp] * 4 + [_i] * 10 + [_vp]),
     "skb_kv_append": (_i, [_vp] * 5 + [_i] * 8 + [_vp]),
     "skb_status_string": (_c.c_char_p, [_i]),

@@ -60,15 +60,16 @@ class FlashAttentionFunction(torch.autograd.Function):
         if sm_scale is None:
             sm_scale = 1.0 / math.sqrt(q.shape[-1])
         ctx.sm_scale = sm_scale
-        q_c, k_c, v_c = ensure_contiguous(q), ensure_contiguous(k), ensure_contiguous(v)
-        out, lse = flash_attn_fwd(q_c, k_c, v_c, is_causal=ctx.is_causal, sm_scale=sm_scale)
-        ctx.save_for_backward(q_c, k_c, v_c, out, lse)
+        # Strided views go to the launcher as they are: the tensor-core kernels read them in place, and the
+        # launcher copies (as the reference does here, torch/attention.py:38-40) only when they cannot.
+        out, lse = flash_attn_fwd(q, k, v, is_causal=ctx.is_causal, sm_scale=sm_scale)
+        ctx.save_for_backward(q, k, v, out, lse)
         return out
 
     @staticmethod
     def backward(ctx: Any, do):
         q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = flash_attn_bwd(ensure_contiguous(do), q, k, v, out, lse,
+        dq, dk, dv = flash_attn_bwd(do, q, k, v, out, lse,
                                     is_causal=ctx.is_causal, sm_scale=ctx.sm_scale)
         return dq, dk, dv, None, None
 

@@ -84,8 +84,9 @@ __device__ __forceinline__ void red_add(float* addr, float v) {
 // probabilities (numerically) zero.
 template <typename T>
 __global__ void __launch_bounds__(256)
-bwd_prep_kernel(const T* __restrict__ dout, const T* __restrict__ o, const float* __restrict__ lse,
-                float* __restrict__ delta, float* __restrict__ lse2, int Sq, int Sq_pad, int D, size_t bh_count) {
+bwd_prep_kernel(const T* __restrict__ dout, const Strides do_str, const T* __restrict__ o, const Strides o_str,
+                const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2, int Hq, int Sq,
+                int Sq_pad, int D, size_t bh_count) {
   constexpr int VE = Vec16<T>::N;
   const size_t prow = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -97,11 +98,14 @@ bwd_prep_kernel(const T* __restrict__ dout, const T* __restrict__ o, const float
     return;
   }
   const size_t row = bh * Sq + r;
+  const int ib = (int)(bh / Hq), ih = (int)(bh % Hq);
+  const T* do_row = dout + do_str.at(ib, ih, r);
+  const T* o_row = o + o_str.at(ib, ih, r);
   float s = 0.f;
   for (int c = lane * VE; c < D; c += 32 * VE) {
     float a[VE], b2[VE];
-    load_vec16<T>(dout + row * D + c, a);
-    load_vec16<T>(o + row * D + c, b2);
+    load_vec16<T>(do_row + c, a);
+    load_vec16<T>(o_row + c, b2);
 #pragma unroll
     for (int i = 0; i < VE; ++i) s += a[i] * b2[i];
   }
@@ -114,15 +118,20 @@ bwd_prep_kernel(const T* __restrict__ dout, const T* __restrict__ o, const float
   }
 }
 
-// Postprocess: dQ = T(scale * dQ_accumulator)
+// Postprocess: dQ = T(scale * dQ_accumulator); the accumulator is (B*Hq, Sq, D) contiguous, dQ may be strided.
 template <typename T>
 __global__ void __launch_bounds__(256)
-bwd_post_kernel(const float* __restrict__ acc, T* __restrict__ dq, float scale, size_t n4) {
+bwd_post_kernel(const float* __restrict__ acc, T* __restrict__ dq, const Strides dq_str, float scale, int Hq, int Sq,
+                int D, size_t n4) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n4) return;
   const float4 v = reinterpret_cast<const float4*>(acc)[i];
   T out[4] = {from_f<T>(v.x * scale), from_f<T>(v.y * scale), from_f<T>(v.z * scale), from_f<T>(v.w * scale)};
-  *reinterpret_cast<uint2*>(dq + i * 4) = *reinterpret_cast<uint2*>(out);
+  const size_t e = i * 4, row = e / D;
+  const int c = (int)(e % D);
+  const size_t bh = row / Sq;
+  T* dst = dq + dq_str.at((int)(bh / Hq), (int)(bh % Hq), (long long)(row % Sq)) + c;
+  *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<uint2*>(out);
 }
 
 
@@ -131,7 +140,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
            const float* __restrict__ lse2, const float* __restrict__ delta, float* __restrict__ dq_acc,
-           T* __restrict__ dk, T* __restrict__ dv, int Hq, int Hkv, int Sq, int Sk, int Sq_pad, int D, int causal,
+           T* __restrict__ dk, const Strides dk_str, T* __restrict__ dv, const Strides dv_str, int Hq, int Hkv,
+           int Sq, int Sk, int Sq_pad, int D, int causal,
            float scale, float scale_log2) {
   // The tiles are 128 columns wide; D <= 128 (a multiple of 8) is the head dimension in memory.  The tensor
   // maps cover D columns, so the bulk copies zero columns [D, 128) of Q, K, V and dO, which leaves every
@@ -202,8 +212,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ptx::prefetch_tmap(&tm_q); ptx::prefetch_tmap(&tm_k); ptx::prefetch_tmap(&tm_v); ptx::prefetch_tmap(&tm_do);
       ptx::mbar_expect_tx(bar(B_KV_FULL), 2 * kBwdTileBytes);
       for (int h = 0; h < 2; ++h) {
-        ptx::tma_load_3d(sK + h * kBwdBox, &tm_k, h * 64, kv0, b * Hkv + hkv, bar(B_KV_FULL));
-        ptx::tma_load_3d(sV + h * kBwdBox, &tm_v, h * 64, kv0, b * Hkv + hkv, bar(B_KV_FULL));
+        ptx::tma_load_4d(sK + h * kBwdBox, &tm_k, h * 64, kv0, hkv, b, bar(B_KV_FULL));
+        ptx::tma_load_4d(sV + h * kBwdBox, &tm_v, h * 64, kv0, hkv, b, bar(B_KV_FULL));
       }
       bool ok = true;
       for (int u = 0; u < n_run && ok; ++u) {
@@ -213,13 +223,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         ok = ptx::mbar_wait(bar(B_Q_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(B_Q_FULL + st), kBwdQTile + 512);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sQ(st) + h * kBwdQBox, &tm_q, h * 64, q0, bh, bar(B_Q_FULL + st));
+        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sQ(st) + h * kBwdQBox, &tm_q, h * 64, q0, head_of(u), b, bar(B_Q_FULL + st));
         bulk_load_1d(sStat0 + st * 512, lse2 + (size_t)bh * Sq_pad + q0, 256, bar(B_Q_FULL + st));
         bulk_load_1d(sStat0 + st * 512 + 256, delta + (size_t)bh * Sq_pad + q0, 256, bar(B_Q_FULL + st));
         ok = ptx::mbar_wait(bar(B_DO_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(B_DO_FULL + st), kBwdQTile);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sdO(st) + h * kBwdQBox, &tm_do, h * 64, q0, bh, bar(B_DO_FULL + st));
+        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sdO(st) + h * kBwdQBox, &tm_do, h * 64, q0, head_of(u), b, bar(B_DO_FULL + st));
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (7u << 16));
     } else if (warp == 1 && n_run > 0) {
@@ -442,10 +452,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     }
     if (ok) {
       ptx::tc_fence_after();
-      const size_t row = ((size_t)b * Hkv + hkv) * Sk + min(kvidx, Sk - 1);
+      const int krow = min(kvidx, Sk - 1);
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        T* dst = (which == 0 ? dk : dv) + row * D + 64 * w;
+        T* dst = (which == 0 ? dk + dk_str.at(b, hkv, krow) : dv + dv_str.at(b, hkv, krow)) + 64 * w;
         const float mul = which == 0 ? scale : 1.f;
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2) {

@@ -29,6 +29,17 @@ template <> __device__ __forceinline__ __half from_f<__half>(float x) { return _
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
 // Number of elements in one 16-byte vector of T.
+// Element strides of the (batch, head, sequence) dimensions of a 4-D tensor whose last dimension is contiguous.
+struct Strides {
+  long long b, h, s;
+  __host__ __device__ size_t at(int ib, int ih, long long is) const {
+    return (size_t)((long long)ib * b + (long long)ih * h + is * s);
+  }
+};
+inline Strides contiguous_strides(int H, int S, int D) {
+  return Strides{(long long)H * S * D, (long long)S * D, (long long)D};
+}
+
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
 
 // Load 16 bytes (Vec16<T>::N elements) from global memory and widen to fp32.

@@ -64,7 +64,8 @@ __device__ __forceinline__ uint32_t swz(int row, int ch) {
 template <typename T, int HD, int MT>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-              const T* __restrict__ q, const int32_t* __restrict__ seqlens, float* __restrict__ part_o,
+              const T* __restrict__ q, const Strides q_str, const int32_t* __restrict__ seqlens,
+              float* __restrict__ part_o,
               float2* __restrict__ part_ml, int Hq, int Hkv, int Scap, int D, int nsplit, float scale_log2) {
   // D <= HD (a multiple of 8) is the head dimension in memory: the tensor maps cover D columns, so the bulk
   // copies zero columns [D, HD) of the K/V tiles; Q is read and the partial O written D columns wide.
@@ -118,8 +119,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         ptx::mbar_expect_tx(full(st), 2 * TILE);
         const int row = start + j * kTileN;
         for (int h = 0; h < HD / 64; ++h) {
-          ptx::tma_load_3d(sK(st) + h * kBoxBytes, &tm_k, h * 64, row, b * Hkv + hkv, full(st));
-          ptx::tma_load_3d(sV(st) + h * kBoxBytes, &tm_v, h * 64, row, b * Hkv + hkv, full(st));
+          ptx::tma_load_4d(sK(st) + h * kBoxBytes, &tm_k, h * 64, row, hkv, b, full(st));
+          ptx::tma_load_4d(sV(st) + h * kBoxBytes, &tm_v, h * 64, row, hkv, b, full(st));
         }
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (4u << 16));
@@ -136,15 +137,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   uint32_t qf[KS][4];
   {
-    const T* qb = q + ((size_t)b * Hq + (size_t)hkv * G) * D;
+    const T* qb = q + q_str.at(b, hkv * G, 0);   // rows of the group: q_str.h elements apart
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
       const int c = 16 * kk + 2 * tq;
       const bool lo = r_lo < G, hi = r_hi < G, c0 = c < D, c1 = c + 8 < D;
-      qf[kk][0] = lo && c0 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * D + c) : 0u;
-      qf[kk][1] = hi && c0 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * D + c) : 0u;
-      qf[kk][2] = lo && c1 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * D + c + 8) : 0u;
-      qf[kk][3] = hi && c1 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * D + c + 8) : 0u;
+      qf[kk][0] = lo && c0 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * q_str.h + c) : 0u;
+      qf[kk][1] = hi && c0 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * q_str.h + c) : 0u;
+      qf[kk][2] = lo && c1 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_lo * q_str.h + c + 8) : 0u;
+      qf[kk][3] = hi && c1 ? *reinterpret_cast<const uint32_t*>(qb + (size_t)r_hi * q_str.h + c + 8) : 0u;
     }
   }
   float oacc[NT_O][4];

@@ -90,8 +90,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // ------------------------------------------------------------------ TMA producer
       ptx::prefetch_tmap(&tm_q); ptx::prefetch_tmap(&tm_k); ptx::prefetch_tmap(&tm_v);
       ptx::mbar_expect_tx(bar(Q_FULL), kTile);
-      // rows = query heads of this group (q viewed as (B*Hq, D)); rows >= G are other heads or zero fill
-      for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sQ + h * kBoxBytes, &tm_q, h * 64, b * Hq + hkv * G, 0, bar(Q_FULL));
+      // rows = query heads of this group (q viewed as {D, Hq, B}); rows >= G are other heads or zero fill
+      for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sQ + h * kBoxBytes, &tm_q, h * 64, hkv * G, b, bar(Q_FULL));
       bool ok = true;
       for (int j = 0; j < nt && ok; ++j) {
         const int st = j % kStages;
@@ -100,11 +100,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ok = ptx::mbar_wait(bar(K_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(K_FULL + st), kTile);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sK(st) + h * kBoxBytes, &tm_k, h * 64, row, b * Hkv + hkv, bar(K_FULL + st));
+        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sK(st) + h * kBoxBytes, &tm_k, h * 64, row, hkv, b, bar(K_FULL + st));
         ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(V_FULL + st), kTile);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sV(st) + h * kBoxBytes, &tm_v, h * 64, row, b * Hkv + hkv, bar(V_FULL + st));
+        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sV(st) + h * kBoxBytes, &tm_v, h * 64, row, hkv, b, bar(V_FULL + st));
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (13u << 16));
     }

@@ -70,7 +70,7 @@ fwd2_kernel(const T* __restrict__ q, const __grid_constant__ CUtensorMap tm_k, c
   const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;      // heaviest (latest) causal tiles first
   const int hq = blockIdx.y, b = blockIdx.z;
   const int bhq = b * Hq + hq;
-  const int bhkv = b * Hkv + hq / (Hq / Hkv);
+  const int hkv = hq / (Hq / Hkv);
   const int row0 = qt * 128;
   const int shift = Sk - Sq;
   int lim = Sk;
@@ -108,11 +108,11 @@ fwd2_kernel(const T* __restrict__ q, const __grid_constant__ CUtensorMap tm_k, c
         ok = ptx::mbar_wait(bar(F2_K_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(F2_K_FULL + st), kF2Tile);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sK(st) + h * kBoxBytes, &tm_k, h * 64, j * 128, bhkv, bar(F2_K_FULL + st));
+        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sK(st) + h * kBoxBytes, &tm_k, h * 64, j * 128, hkv, b, bar(F2_K_FULL + st));
         ok = ptx::mbar_wait(bar(F2_V_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(F2_V_FULL + st), kF2Tile);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sV(st) + h * kBoxBytes, &tm_v, h * 64, j * 128, bhkv, bar(F2_V_FULL + st));
+        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sV(st) + h * kBoxBytes, &tm_v, h * 64, j * 128, hkv, b, bar(F2_V_FULL + st));
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (10u << 16));
     } else if (warp == 1) {

@@ -518,7 +518,7 @@ constexpr int kMaxSplits = 256;
 template <typename T>
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml, T* __restrict__ o,
-                      float* __restrict__ lse, int D, int nsplit) {
+                      const Strides o_str, float* __restrict__ lse, int Hq, int D, int nsplit) {
   __shared__ float s_w[kMaxSplits];
   __shared__ float s_ML[2];
   const size_t bh = blockIdx.x;
@@ -542,10 +542,11 @@ decode_combine_kernel(const float* __restrict__ part_o, const float2* __restrict
   __syncthreads();
   const float M = s_ML[0], L = s_ML[1];
   const float inv = L > 0.f ? 1.f / L : 0.f;
+  T* orow = o + o_str.at((int)(bh / Hq), (int)(bh % Hq), 0);
   for (int d = threadIdx.x; d < D; d += 128) {
     float sum = 0.f;
     for (int s = 0; s < nsplit; ++s) sum += part_o[(bh * nsplit + s) * D + d] * s_w[s];
-    o[bh * D + d] = from_f<T>(sum * inv);
+    orow[d] = from_f<T>(sum * inv);
   }
   if (lse != nullptr && threadIdx.x == 0) lse[bh] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
 }

@@ -127,7 +127,7 @@ int decode_general(const void* q, const void* kc, const void* vc, const int32_t*
   else if (ch <= 32) rc = launch_decode_general<T, 32, 1>(q, kc, vc, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st);
   else rc = launch_decode_general<T, 32, 2>(q, kc, vc, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st);
   if (rc) return rc;
-  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, lse, D, nsplit);
+  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, contiguous_strides(Hq, 1, D), lse, Hq, D, nsplit);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -149,12 +149,11 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
-// (BH, S, D) 16-bit tensor viewed as a 3-D map {D, S, BH}; boxes of 64 columns x box_rows rows, 128-byte swizzle,
-// out-of-range rows read as zero.
-int make_map_3d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, size_t BH, int box_rows = 128) {
-  // The driver call below needs the device's primary context current on THIS host thread.  A thread
-  // that has only inherited a device ordinal (e.g. an autograd worker) may not have it bound yet;
-  // cudaSetDevice on the current ordinal binds it.
+// The driver call that encodes a tensor map needs the device's primary context current on THIS host
+// thread.  A thread that has only inherited a device ordinal (e.g. an autograd worker) may not have it
+// bound yet; cudaSetDevice on the current ordinal binds it.
+int encode_map(CUtensorMap* map, int dtype, const void* ptr, int rank, const cuuint64_t* dims,
+               const cuuint64_t* strides_bytes, const cuuint32_t* box) {
   int dev = 0;
   SKB_CUDA(cudaGetDevice(&dev));
   SKB_CUDA(cudaSetDevice(dev));
@@ -163,18 +162,45 @@ int make_map_3d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, size
     snprintf(tl_cuda_err, sizeof(tl_cuda_err), "cuTensorMapEncodeTiled entry point not available");
     return SKB_ERR_CUDA;
   }
-  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
-  const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
-  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, dtype == SKB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
-                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dtype == SKB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                   (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides_bytes, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     snprintf(tl_cuda_err, sizeof(tl_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return SKB_ERR_CUDA;
   }
   return SKB_OK;
+}
+
+// (B, H, S, D) 16-bit tensor with element strides `str` (D contiguous) as a 4-D map {D, S, H, B}: boxes of
+// 64 columns x box_rows rows, 128-byte swizzle, out-of-range rows and columns read as zero.
+int make_map_4d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, int H, int B, const Strides& str,
+                int box_rows = 128) {
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  // a dimension of extent 1 is never stepped over; give it a harmless legal stride
+  auto sb = [&](long long e, int extent) { return (cuuint64_t)((extent > 1 ? e : (long long)D) * 2); };
+  const cuuint64_t strides[3] = {sb(str.s, S), sb(str.h, H), sb(str.b, B)};
+  const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  return encode_map(map, dtype, ptr, 4, dims, strides, box);
+}
+
+// Decode queries (B, Hq, 1, D) as a 3-D map {D, Hq, B}: one box = the 128 heads from a given head on.
+int make_map_q_heads(CUtensorMap* map, int dtype, const void* ptr, int D, int Hq, int B, const Strides& str) {
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Hq, (cuuint64_t)B};
+  const cuuint64_t strides[2] = {(cuuint64_t)((Hq > 1 ? str.h : (long long)D) * 2),
+                                 (cuuint64_t)((B > 1 ? str.b : (long long)D) * 2)};
+  const cuuint32_t box[3] = {64, 128, 1};
+  return encode_map(map, dtype, ptr, 3, dims, strides, box);
+}
+
+// What the bulk-copy engine and the 16-byte vector stores need from a strided 16-bit tensor.
+bool strides_ok(const void* p, const Strides& s, int B, int H, int S) {
+  if (!aligned16(p)) return false;
+  if ((B > 1 && (s.b <= 0 || s.b % 8 != 0)) || (H > 1 && (s.h <= 0 || s.h % 8 != 0)) || (S > 1 && (s.s <= 0 || s.s % 8 != 0)))
+    return false;
+  return true;
 }
 
 bool fwd_sm100_covers(int D, int dtype, float scale) {
@@ -184,18 +210,19 @@ bool fwd_sm100_covers(int D, int dtype, float scale) {
 }
 
 template <typename T, int HD>
-int launch_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
-                     int Sk, int D, int causal, float scale, cudaStream_t st) {
+int launch_fwd_sm100(const void* q, const Strides& qs, const void* k, const Strides& ks, const void* v, const Strides& vs,
+                     void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Sq, int Sk, int D, int causal,
+                     float scale, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   const int dt = DtypeOf<T>::value;
-  if (int rc = make_map_3d(&mq, dt, q, D, Sq, (size_t)B * Hq)) return rc;
-  if (int rc = make_map_3d(&mk, dt, k, D, Sk, (size_t)B * Hkv)) return rc;
-  if (int rc = make_map_3d(&mv, dt, v, D, Sk, (size_t)B * Hkv)) return rc;
+  if (int rc = make_map_4d(&mq, dt, q, D, Sq, Hq, B, qs)) return rc;
+  if (int rc = make_map_4d(&mk, dt, k, D, Sk, Hkv, B, ks)) return rc;
+  if (int rc = make_map_4d(&mv, dt, v, D, Sk, Hkv, B, vs)) return rc;
   auto kern = sm100::fwd_kernel<T, HD>;
   constexpr size_t smem = sm100::fwd_smem_bytes<HD>();
   if (int rc = set_smem(kern, smem)) return rc;
   dim3 grid(cdiv(Sq, 2 * sm100::kTileM), Hq, B);
-  kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, lse, Hq, Hkv, Sq, Sk, D, causal, scale * kLog2e);
+  kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, os, lse, Hq, Hkv, Sq, Sk, D, causal, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -205,8 +232,8 @@ int launch_fwd2_sm100(const void* q, const void* k, const void* v, void* o, floa
                       int Sk, int causal, float scale, cudaStream_t st) {
   CUtensorMap mk, mv;
   const int dt = DtypeOf<T>::value;
-  if (int rc = make_map_3d(&mk, dt, k, 128, Sk, (size_t)B * Hkv)) return rc;
-  if (int rc = make_map_3d(&mv, dt, v, 128, Sk, (size_t)B * Hkv)) return rc;
+  if (int rc = make_map_4d(&mk, dt, k, 128, Sk, Hkv, B, contiguous_strides(Hkv, Sk, 128))) return rc;
+  if (int rc = make_map_4d(&mv, dt, v, 128, Sk, Hkv, B, contiguous_strides(Hkv, Sk, 128))) return rc;
   auto kern = sm100::fwd2_kernel<T>;
   if (int rc = set_smem(kern, sm100::kF2SmemBytes)) return rc;
   dim3 grid(cdiv(Sq, 128), Hq, B);
@@ -236,10 +263,16 @@ BwdWs bwd_sm100_ws(int B, int Hq, int Sq, int D) {
   return w;
 }
 
+// The 4-D tensors of the backward pass: pointer + element strides each.
+struct BwdTensors {
+  const void *dout, *q, *k, *v, *o;
+  void *dq, *dk, *dv;
+  Strides dos, qs, ks, vs, os, dqs, dks, dvs;
+};
+
 template <typename T>
-int launch_bwd_sm100(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
-                     void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk, int D, int causal, float scale,
-                     void* workspace, cudaStream_t st) {
+int launch_bwd_sm100(const BwdTensors& t, const float* lse, int B, int Hq, int Hkv, int Sq, int Sk, int D, int causal,
+                     float scale, void* workspace, cudaStream_t st) {
   const BwdWs w = bwd_sm100_ws(B, Hq, Sq, D);
   float* delta = (float*)((char*)workspace + w.delta_off);
   float* lse2 = (float*)((char*)workspace + w.lse2_off);
@@ -248,23 +281,24 @@ int launch_bwd_sm100(const void* dout, const void* q, const void* k, const void*
   const size_t bh = (size_t)B * Hq;
   CUtensorMap mq, mk, mv, mdo;
   const int dt = DtypeOf<T>::value;
-  if (int rc = make_map_3d(&mq, dt, q, D, Sq, bh, sm100::kBwdQ)) return rc;
-  if (int rc = make_map_3d(&mdo, dt, dout, D, Sq, bh, sm100::kBwdQ)) return rc;
-  if (int rc = make_map_3d(&mk, dt, k, D, Sk, (size_t)B * Hkv)) return rc;
-  if (int rc = make_map_3d(&mv, dt, v, D, Sk, (size_t)B * Hkv)) return rc;
+  if (int rc = make_map_4d(&mq, dt, t.q, D, Sq, Hq, B, t.qs, sm100::kBwdQ)) return rc;
+  if (int rc = make_map_4d(&mdo, dt, t.dout, D, Sq, Hq, B, t.dos, sm100::kBwdQ)) return rc;
+  if (int rc = make_map_4d(&mk, dt, t.k, D, Sk, Hkv, B, t.ks)) return rc;
+  if (int rc = make_map_4d(&mv, dt, t.v, D, Sk, Hkv, B, t.vs)) return rc;
 
   const size_t prows = bh * sq_pad;
-  sm100::bwd_prep_kernel<T><<<(unsigned)((prows + 7) / 8), 256, 0, st>>>((const T*)dout, (const T*)o, lse, delta, lse2,
-                                                                        Sq, sq_pad, D, bh);
+  sm100::bwd_prep_kernel<T><<<(unsigned)((prows + 7) / 8), 256, 0, st>>>((const T*)t.dout, t.dos, (const T*)t.o, t.os, lse,
+                                                                        delta, lse2, Hq, Sq, sq_pad, D, bh);
   SKB_CUDA(cudaGetLastError());
   SKB_CUDA(cudaMemsetAsync(dq_acc, 0, bh * Sq * D * sizeof(float), st));
   auto kern = sm100::bwd_kernel<T>;
   if (int rc = set_smem(kern, sm100::kBwdSmemBytes)) return rc;
   kern<<<dim3(cdiv(Sk, 128), Hkv, B), sm100::kBwdThreads, sm100::kBwdSmemBytes, st>>>(
-      mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)dk, (T*)dv, Hq, Hkv, Sq, Sk, sq_pad, D, causal, scale, scale * kLog2e);
+      mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)t.dk, t.dks, (T*)t.dv, t.dvs, Hq, Hkv, Sq, Sk, sq_pad, D, causal, scale,
+      scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   const size_t n4 = bh * Sq * D / 4;
-  sm100::bwd_post_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_acc, (T*)dq, scale, n4);
+  sm100::bwd_post_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_acc, (T*)t.dq, t.dqs, scale, Hq, Sq, D, n4);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -279,47 +313,49 @@ bool decode_group_covers(int Hq, int Hkv, int D, int dtype) {
 bool decode_uses_tcgen05(int Hq, int Hkv, int D) { return D > 64 && D <= 128 && Hq / Hkv > 16; }
 
 template <typename T, int HD, int MT>
-int launch_decode_group(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int32_t* lens, float* part_o,
-                        float2* part_ml, int B, int Hq, int Hkv, int Scap, int D, int nsplit, float scale, cudaStream_t st) {
+int launch_decode_group(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const Strides& qs,
+                        const int32_t* lens, float* part_o, float2* part_ml, int B, int Hq, int Hkv, int Scap, int D,
+                        int nsplit, float scale, cudaStream_t st) {
   auto kern = dgrp::decode_kernel<T, HD, MT>;
   constexpr size_t smem = dgrp::smem_bytes<HD>();
   if (int rc = set_smem(kern, smem)) return rc;
-  kern<<<dim3(nsplit, Hkv, B), dgrp::kThreads, smem, st>>>(mk, mv, (const T*)q, lens, part_o, part_ml, Hq, Hkv, Scap,
+  kern<<<dim3(nsplit, Hkv, B), dgrp::kThreads, smem, st>>>(mk, mv, (const T*)q, qs, lens, part_o, part_ml, Hq, Hkv, Scap,
                                                           D, nsplit, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
 
 template <typename T>
-int decode_group(const void* q, const void* kc, const void* vc, const int32_t* lens, void* o, float* lse, int B, int Hq,
-                 int Hkv, int Scap, int D, int nsplit, float scale, float* part_o, float2* part_ml, cudaStream_t st) {
+int decode_group(const void* q, const Strides& qs, const void* kc, const Strides& ks, const void* vc, const Strides& vs,
+                 const int32_t* lens, void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Scap, int D,
+                 int nsplit, float scale, float* part_o, float2* part_ml, cudaStream_t st) {
   const int dt = DtypeOf<T>::value;
   const int G = Hq / Hkv;
   int rc;
   if (decode_uses_tcgen05(Hq, Hkv, D)) {
     // wide groups: tcgen05 kernel with the group's heads as the MMA M dimension (decode_tc.cuh)
     CUtensorMap mq, mk128, mv128;
-    if (int r2 = make_map_3d(&mq, dt, q, D, B * Hq, 1)) return r2;
-    if (int r2 = make_map_3d(&mk128, dt, kc, D, Scap, (size_t)B * Hkv)) return r2;
-    if (int r2 = make_map_3d(&mv128, dt, vc, D, Scap, (size_t)B * Hkv)) return r2;
+    if (int r2 = make_map_q_heads(&mq, dt, q, D, Hq, B, qs)) return r2;
+    if (int r2 = make_map_4d(&mk128, dt, kc, D, Scap, Hkv, B, ks)) return r2;
+    if (int r2 = make_map_4d(&mv128, dt, vc, D, Scap, Hkv, B, vs)) return r2;
     auto kern = dtc::decode_kernel<T>;
     if (int r2 = set_smem(kern, dtc::kSmemBytes)) return r2;
     kern<<<dim3(nsplit, Hkv, B), dtc::kThreads, dtc::kSmemBytes, st>>>(mq, mk128, mv128, lens, part_o, part_ml, Hq, Hkv,
                                                                       Scap, D, nsplit, scale * kLog2e);
     SKB_CUDA(cudaGetLastError());
-    general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, lse, D, nsplit);
+    general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, os, lse, Hq, D, nsplit);
     SKB_CUDA(cudaGetLastError());
     return SKB_OK;
   }
   CUtensorMap mk, mv;
-  if (int r2 = make_map_3d(&mk, dt, kc, D, Scap, (size_t)B * Hkv, dgrp::kTileN)) return r2;
-  if (int r2 = make_map_3d(&mv, dt, vc, D, Scap, (size_t)B * Hkv, dgrp::kTileN)) return r2;
-#define SKB_DG(HD_, MT_) launch_decode_group<T, HD_, MT_>(mk, mv, q, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st)
+  if (int r2 = make_map_4d(&mk, dt, kc, D, Scap, Hkv, B, ks, dgrp::kTileN)) return r2;
+  if (int r2 = make_map_4d(&mv, dt, vc, D, Scap, Hkv, B, vs, dgrp::kTileN)) return r2;
+#define SKB_DG(HD_, MT_) launch_decode_group<T, HD_, MT_>(mk, mv, q, qs, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st)
   if (D <= 64) rc = G <= 16 ? SKB_DG(64, 1) : (G <= 32 ? SKB_DG(64, 2) : SKB_DG(64, 4));
   else rc = G <= 16 ? SKB_DG(128, 1) : (G <= 32 ? SKB_DG(128, 2) : SKB_DG(128, 4));
 #undef SKB_DG
   if (rc) return rc;
-  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, lse, D, nsplit);
+  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, os, lse, Hq, D, nsplit);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -381,33 +417,67 @@ int skb_attn_fwd_uses_sm100(int B, int Hq, int Hkv, int Sq, int Sk, int D, int d
   return fwd_sm100_covers(D, dtype, 1.f) && Sq >= 128 && Sk >= 128;
 }
 
-int skb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
-                 int Sk, int D, int dtype, int causal, float scale, int impl, void* stream) {
+namespace {
+Strides strides_from(const int64_t* p) { return Strides{(long long)p[0], (long long)p[1], (long long)p[2]}; }
+bool same_strides(const Strides& a, const Strides& b, int B, int H, int S) {
+  return (B == 1 || a.b == b.b) && (H == 1 || a.h == b.h) && (S == 1 || a.s == b.s);
+}
+
+int attn_fwd_impl(const void* q, const Strides& qs, const void* k, const Strides& ks, const void* v, const Strides& vs,
+                  void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype,
+                  int causal, float scale, int impl, cudaStream_t st) {
   if (!q || !k || !v || !o || !lse) return SKB_ERR_NULL;
   if (int rc = check_common(B, Hq, Hkv, Sq, Sk, D, dtype)) return rc;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SKB_ERR_ALIGN;
-  cudaStream_t st = (cudaStream_t)stream;
+  const bool dense = same_strides(qs, contiguous_strides(Hq, Sq, D), B, Hq, Sq) &&
+                     same_strides(ks, contiguous_strides(Hkv, Sk, D), B, Hkv, Sk) &&
+                     same_strides(vs, contiguous_strides(Hkv, Sk, D), B, Hkv, Sk) &&
+                     same_strides(os, contiguous_strides(Hq, Sq, D), B, Hq, Sq);
   const bool covers = fwd_sm100_covers(D, dtype, scale);
   if ((impl == SKB_IMPL_SM100 || impl == 3) && !covers) return SKB_ERR_UNSUPPORTED;
   const bool gen2 = impl == 3;   // selector for the alternative forward (Q resident in TMEM, fwd2_sm100.cuh), for A/B timing
   if (gen2) impl = SKB_IMPL_SM100;
   const bool use_tc = impl == SKB_IMPL_SM100 || (impl == SKB_IMPL_AUTO && covers && Sq >= 128 && Sk >= 128);
+  if (!dense) {
+    // strided tensors: only the bulk-copy kernels can address them
+    if (!use_tc || gen2) return SKB_ERR_UNSUPPORTED;
+    if (!strides_ok(q, qs, B, Hq, Sq) || !strides_ok(k, ks, B, Hkv, Sk) || !strides_ok(v, vs, B, Hkv, Sk) ||
+        !strides_ok(o, os, B, Hq, Sq))
+      return SKB_ERR_ALIGN;
+  }
   if (use_tc && D == 128 && gen2) {
     if (dtype == SKB_F16) return launch_fwd2_sm100<__half>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
     return launch_fwd2_sm100<__nv_bfloat16>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
   }
   if (use_tc) {
-    if (dtype == SKB_F16)
-      return D <= 64 ? launch_fwd_sm100<__half, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st)
-                     : launch_fwd_sm100<__half, 128>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
-    return D <= 64 ? launch_fwd_sm100<__nv_bfloat16, 64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st)
-                   : launch_fwd_sm100<__nv_bfloat16, 128>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+#define SKB_FWD(T_, HD_) launch_fwd_sm100<T_, HD_>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st)
+    if (dtype == SKB_F16) return D <= 64 ? SKB_FWD(__half, 64) : SKB_FWD(__half, 128);
+    return D <= 64 ? SKB_FWD(__nv_bfloat16, 64) : SKB_FWD(__nv_bfloat16, 128);
+#undef SKB_FWD
   }
   switch (dtype) {
     case SKB_F32: return fwd_general<float>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
     case SKB_F16: return fwd_general<__half>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
     default: return fwd_general<__nv_bfloat16>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
   }
+}
+}  // namespace
+
+int skb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
+                 int Sk, int D, int dtype, int causal, float scale, int impl, void* stream) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || Sq < 1 || Sk < 1 || D < 1) return SKB_ERR_SHAPE;
+  const Strides qs = contiguous_strides(Hq, Sq, D), ks = contiguous_strides(Hkv, Sk, D);
+  return attn_fwd_impl(q, qs, k, ks, v, ks, o, qs, lse, B, Hq, Hkv, Sq, Sk, D, dtype, causal, scale, impl,
+                       (cudaStream_t)stream);
+}
+
+int skb_attn_fwd_strided(const void* q, const int64_t* q_strides, const void* k, const int64_t* k_strides, const void* v,
+                         const int64_t* v_strides, void* o, const int64_t* o_strides, float* lse, int B, int Hq, int Hkv,
+                         int Sq, int Sk, int D, int dtype, int causal, float scale, int impl, void* stream) {
+  if (!q_strides || !k_strides || !v_strides || !o_strides) return SKB_ERR_NULL;
+  return attn_fwd_impl(q, strides_from(q_strides), k, strides_from(k_strides), v, strides_from(v_strides), o,
+                       strides_from(o_strides), lse, B, Hq, Hkv, Sq, Sk, D, dtype, causal, scale, impl,
+                       (cudaStream_t)stream);
 }
 
 size_t skb_attn_bwd_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype, int impl) {
@@ -421,31 +491,70 @@ size_t skb_attn_bwd_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Sk, int 
   return general;
 }
 
-int skb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
-                 void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype, int causal,
-                 float scale, int impl, void* workspace, size_t workspace_bytes, void* stream) {
-  if (!dout || !q || !k || !v || !o || !lse || !dq || !dk || !dv) return SKB_ERR_NULL;
+namespace {
+int attn_bwd_impl(const BwdTensors& t, const float* lse, int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype,
+                  int causal, float scale, int impl, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!t.dout || !t.q || !t.k || !t.v || !t.o || !lse || !t.dq || !t.dk || !t.dv) return SKB_ERR_NULL;
   if (int rc = check_common(B, Hq, Hkv, Sq, Sk, D, dtype)) return rc;
-  if (!aligned16(dout) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dq) ||
-      !aligned16(dk) || !aligned16(dv))
+  if (!aligned16(t.dout) || !aligned16(t.q) || !aligned16(t.k) || !aligned16(t.v) || !aligned16(t.o) ||
+      !aligned16(t.dq) || !aligned16(t.dk) || !aligned16(t.dv))
     return SKB_ERR_ALIGN;
+  const Strides cq = contiguous_strides(Hq, Sq, D), ck = contiguous_strides(Hkv, Sk, D);
+  const bool dense = same_strides(t.dos, cq, B, Hq, Sq) && same_strides(t.qs, cq, B, Hq, Sq) &&
+                     same_strides(t.os, cq, B, Hq, Sq) && same_strides(t.dqs, cq, B, Hq, Sq) &&
+                     same_strides(t.ks, ck, B, Hkv, Sk) && same_strides(t.vs, ck, B, Hkv, Sk) &&
+                     same_strides(t.dks, ck, B, Hkv, Sk) && same_strides(t.dvs, ck, B, Hkv, Sk);
   const bool covers = bwd_sm100_covers(D, dtype);
   if (impl == SKB_IMPL_SM100 && !covers) return SKB_ERR_UNSUPPORTED;
   if (!workspace || !aligned16(workspace) ||
       workspace_bytes < skb_attn_bwd_workspace_bytes(B, Hq, Hkv, Sq, Sk, D, dtype, impl))
     return SKB_ERR_WORKSPACE;
-  cudaStream_t st = (cudaStream_t)stream;
-  if (impl == SKB_IMPL_SM100 || (impl == SKB_IMPL_AUTO && covers && Sq >= 128 && Sk >= 128)) {
-    if (dtype == SKB_F16)
-      return launch_bwd_sm100<__half>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, workspace, st);
-    return launch_bwd_sm100<__nv_bfloat16>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, workspace, st);
+  const bool use_tc = impl == SKB_IMPL_SM100 || (impl == SKB_IMPL_AUTO && covers && Sq >= 128 && Sk >= 128);
+  if (!dense) {
+    if (!use_tc) return SKB_ERR_UNSUPPORTED;
+    if (!strides_ok(t.dout, t.dos, B, Hq, Sq) || !strides_ok(t.q, t.qs, B, Hq, Sq) || !strides_ok(t.o, t.os, B, Hq, Sq) ||
+        !strides_ok(t.dq, t.dqs, B, Hq, Sq) || !strides_ok(t.k, t.ks, B, Hkv, Sk) || !strides_ok(t.v, t.vs, B, Hkv, Sk) ||
+        !strides_ok(t.dk, t.dks, B, Hkv, Sk) || !strides_ok(t.dv, t.dvs, B, Hkv, Sk))
+      return SKB_ERR_ALIGN;
+  }
+  if (use_tc) {
+    if (dtype == SKB_F16) return launch_bwd_sm100<__half>(t, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, workspace, st);
+    return launch_bwd_sm100<__nv_bfloat16>(t, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, workspace, st);
   }
   float* delta = (float*)workspace;
+#define SKB_BWDG(T_) bwd_general<T_>(t.dout, t.q, t.k, t.v, t.o, lse, t.dq, t.dk, t.dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st)
   switch (dtype) {
-    case SKB_F32: return bwd_general<float>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);
-    case SKB_F16: return bwd_general<__half>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);
-    default: return bwd_general<__nv_bfloat16>(dout, q, k, v, o, lse, dq, dk, dv, B, Hq, Hkv, Sq, Sk, D, causal, scale, delta, st);
+    case SKB_F32: return SKB_BWDG(float);
+    case SKB_F16: return SKB_BWDG(__half);
+    default: return SKB_BWDG(__nv_bfloat16);
   }
+#undef SKB_BWDG
+}
+}  // namespace
+
+int skb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                 void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk, int D, int dtype, int causal,
+                 float scale, int impl, void* workspace, size_t workspace_bytes, void* stream) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || Sq < 1 || Sk < 1 || D < 1) return SKB_ERR_SHAPE;
+  const Strides cq = contiguous_strides(Hq, Sq, D), ck = contiguous_strides(Hkv, Sk, D);
+  const BwdTensors t{dout, q, k, v, o, dq, dk, dv, cq, cq, ck, ck, cq, cq, ck, ck};
+  return attn_bwd_impl(t, lse, B, Hq, Hkv, Sq, Sk, D, dtype, causal, scale, impl, workspace, workspace_bytes,
+                       (cudaStream_t)stream);
+}
+
+int skb_attn_bwd_strided(const void* dout, const int64_t* dout_strides, const void* q, const int64_t* q_strides,
+                         const void* k, const int64_t* k_strides, const void* v, const int64_t* v_strides, const void* o,
+                         const int64_t* o_strides, const float* lse, void* dq, const int64_t* dq_strides, void* dk,
+                         const int64_t* dk_strides, void* dv, const int64_t* dv_strides, int B, int Hq, int Hkv, int Sq,
+                         int Sk, int D, int dtype, int causal, float scale, int impl, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  if (!dout_strides || !q_strides || !k_strides || !v_strides || !o_strides || !dq_strides || !dk_strides || !dv_strides)
+    return SKB_ERR_NULL;
+  const BwdTensors t{dout, q, k, v, o, dq, dk, dv,
+                     strides_from(dout_strides), strides_from(q_strides), strides_from(k_strides), strides_from(v_strides),
+                     strides_from(o_strides), strides_from(dq_strides), strides_from(dk_strides), strides_from(dv_strides)};
+  return attn_bwd_impl(t, lse, B, Hq, Hkv, Sq, Sk, D, dtype, causal, scale, impl, workspace, workspace_bytes,
+                       (cudaStream_t)stream);
 }
 
 int skb_decode_num_splits(int B, int Hq, int Hkv, int Scap, int D, int dtype, int sm_count) {
@@ -482,33 +591,65 @@ size_t skb_decode_workspace_bytes(int B, int Hq, int Hkv, int Scap, int D, int d
   return align_up(n * D * sizeof(float), 256) + align_up(n * sizeof(float2), 256);
 }
 
-int skb_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* cache_seqlens, void* o,
-               float* lse, int B, int Hq, int Hkv, int Scap, int D, int dtype, float scale, int num_splits, int impl,
-               void* workspace, size_t workspace_bytes, void* stream) {
+namespace {
+int decode_impl(const void* q, const Strides& qs, const void* k_cache, const Strides& ks, const void* v_cache,
+                const Strides& vs, const int32_t* cache_seqlens, void* o, const Strides& os, float* lse, int B, int Hq,
+                int Hkv, int Scap, int D, int dtype, float scale, int num_splits, int impl, void* workspace,
+                size_t workspace_bytes, cudaStream_t st) {
   if (!q || !k_cache || !v_cache || !o) return SKB_ERR_NULL;
   if (int rc = check_common(B, Hq, Hkv, 1, Scap, D, dtype)) return rc;
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o)) return SKB_ERR_ALIGN;
+  const bool dense = same_strides(qs, contiguous_strides(Hq, 1, D), B, Hq, 1) &&
+                     same_strides(os, contiguous_strides(Hq, 1, D), B, Hq, 1) &&
+                     same_strides(ks, contiguous_strides(Hkv, Scap, D), B, Hkv, Scap) &&
+                     same_strides(vs, contiguous_strides(Hkv, Scap, D), B, Hkv, Scap);
   const bool group_ok = decode_group_covers(Hq, Hkv, D, dtype);
   if (impl == SKB_IMPL_SM100 && !group_ok) return SKB_ERR_UNSUPPORTED;
+  const bool use_group = group_ok && impl != SKB_IMPL_GENERAL;
+  if (!dense) {
+    if (!use_group) return SKB_ERR_UNSUPPORTED;
+    if (!strides_ok(q, qs, B, Hq, 1) || !strides_ok(o, os, B, Hq, 1) || !strides_ok(k_cache, ks, B, Hkv, Scap) ||
+        !strides_ok(v_cache, vs, B, Hkv, Scap))
+      return SKB_ERR_ALIGN;
+  }
   if (num_splits <= 0) num_splits = skb_decode_num_splits(B, Hq, Hkv, Scap, D, dtype, 0);
   if (num_splits > skb::general::kMaxSplits) return SKB_ERR_TOO_LARGE;
   if (!workspace || !aligned16(workspace) ||
       workspace_bytes < skb_decode_workspace_bytes(B, Hq, Hkv, Scap, D, dtype, num_splits))
     return SKB_ERR_WORKSPACE;
-  cudaStream_t st = (cudaStream_t)stream;
   const size_t n = (size_t)B * Hq * num_splits;
   float* part_o = (float*)workspace;
   float2* part_ml = (float2*)((char*)workspace + align_up(n * D * sizeof(float), 256));
-  if (group_ok && impl != SKB_IMPL_GENERAL) {
-    if (dtype == SKB_F16)
-      return decode_group<__half>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
-    return decode_group<__nv_bfloat16>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+  if (use_group) {
+#define SKB_DGRP(T_) decode_group<T_>(q, qs, k_cache, ks, v_cache, vs, cache_seqlens, o, os, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st)
+    return dtype == SKB_F16 ? SKB_DGRP(__half) : SKB_DGRP(__nv_bfloat16);
+#undef SKB_DGRP
   }
   switch (dtype) {
     case SKB_F32: return decode_general<float>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
     case SKB_F16: return decode_general<__half>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
     default: return decode_general<__nv_bfloat16>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
   }
+}
+}  // namespace
+
+int skb_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* cache_seqlens, void* o,
+               float* lse, int B, int Hq, int Hkv, int Scap, int D, int dtype, float scale, int num_splits, int impl,
+               void* workspace, size_t workspace_bytes, void* stream) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || Scap < 1 || D < 1) return SKB_ERR_SHAPE;
+  const Strides qs = contiguous_strides(Hq, 1, D), ks = contiguous_strides(Hkv, Scap, D);
+  return decode_impl(q, qs, k_cache, ks, v_cache, ks, cache_seqlens, o, qs, lse, B, Hq, Hkv, Scap, D, dtype, scale,
+                     num_splits, impl, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int skb_decode_strided(const void* q, const int64_t* q_strides, const void* k_cache, const int64_t* k_strides,
+                       const void* v_cache, const int64_t* v_strides, const int32_t* cache_seqlens, void* o,
+                       const int64_t* o_strides, float* lse, int B, int Hq, int Hkv, int Scap, int D, int dtype,
+                       float scale, int num_splits, int impl, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!q_strides || !k_strides || !v_strides || !o_strides) return SKB_ERR_NULL;
+  return decode_impl(q, strides_from(q_strides), k_cache, strides_from(k_strides), v_cache, strides_from(v_strides),
+                     cache_seqlens, o, strides_from(o_strides), lse, B, Hq, Hkv, Scap, D, dtype, scale, num_splits, impl,
+                     workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 int skb_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, const int32_t* cache_seqlens, void* o,

@@ -9,6 +9,7 @@ C ABI of ``libskb200.so`` on torch's current CUDA stream.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 
 import torch
@@ -67,38 +68,98 @@ def _stream(t):
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
-def flash_attn_fwd(q, k, v, is_causal=False, sm_scale=None, impl="auto"):
-    """Returns ``(out, lse)``: out like q, lse fp32 ``(B, H_q, S_q)`` (natural log)."""
+def _addressable(t) -> bool:
+    """True when the strided entry points can take ``t`` as it is: 16-bit, head dim contiguous, every other
+    stride a positive multiple of 8 elements, base 16-byte aligned (rules of ``skb_attn_fwd_strided``)."""
+    if t.dtype not in (torch.float16, torch.bfloat16) or t.stride(-1) != 1 or t.data_ptr() % 16 != 0:
+        return False
+    return all(t.size(i) == 1 or (t.stride(i) > 0 and t.stride(i) % 8 == 0) for i in range(3))
+
+
+def _strides3(t):
+    return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _check_out(out, like, name="out"):
+    if out.shape != like.shape or out.dtype != like.dtype or out.device != like.device:
+        raise ValueError(f"{name} must match q: shape {tuple(like.shape)}, {like.dtype}, {like.device}")
+    return out
+
+
+def flash_attn_fwd(q, k, v, is_causal=False, sm_scale=None, impl="auto", out=None):
+    """Returns ``(out, lse)``: out like q, lse fp32 ``(B, H_q, S_q)`` (natural log).
+
+    q, k, v may be strided views (e.g. ``(B,S,H,D)`` projections seen through ``transpose(1, 2)``): where the
+    tensor-core kernels apply they are read in place through their strides instead of being copied with
+    ``.contiguous()`` as the reference does (``src/stackkernels/torch/attention.py:38-40``).  ``out`` (optional)
+    is a preallocated result tensor of q's shape in any such layout; the default is contiguous, like the
+    reference's."""
     B, H_q, H_kv, S_q, S_k, D = validate_attention_layout(q, k, v)
     dt = _check_device_dtype(q, k, v)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    out = torch.empty_like(q)
+    lib = _lib.load()
+    impl_id = _lib.IMPL_BY_NAME[impl]
     lse = torch.empty((B, H_q, S_q), dtype=torch.float32, device=q.device)
+    if out is not None:
+        _check_out(out, q)
+    dense = all(t.is_contiguous() for t in (q, k, v)) and (out is None or out.is_contiguous())
+    if not dense and all(_addressable(t) for t in (q, k, v)) and (out is None or _addressable(out)):
+        o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        with torch.cuda.device(q.device):
+            rc = lib.skb_attn_fwd_strided(q.data_ptr(), _strides3(q), k.data_ptr(), _strides3(k), v.data_ptr(),
+                                          _strides3(v), o.data_ptr(), _strides3(o), lse.data_ptr(),
+                                          B, H_q, H_kv, S_q, S_k, D, dt, int(bool(is_causal)), float(sm_scale),
+                                          impl_id, _stream(q))
+        if rc != _lib.SKB_ERR_UNSUPPORTED:
+            _raise_for_status(rc, "flash_attn_fwd")
+            return o, lse
+    # contiguous path (the reference's): copy what is not contiguous
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    o = out if out is not None and out.is_contiguous() else torch.empty(q.shape, dtype=q.dtype, device=q.device)
     with torch.cuda.device(q.device):
-        rc = _lib.load().skb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                      B, H_q, H_kv, S_q, S_k, D, dt, int(bool(is_causal)), float(sm_scale),
-                                      _lib.IMPL_BY_NAME[impl], _stream(q))
+        rc = lib.skb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                              B, H_q, H_kv, S_q, S_k, D, dt, int(bool(is_causal)), float(sm_scale),
+                              impl_id, _stream(q))
     _raise_for_status(rc, "flash_attn_fwd")
-    return out, lse
+    if out is not None and o is not out:
+        out.copy_(o)
+        o = out
+    return o, lse
 
 
 def flash_attn_bwd(do, q, k, v, out, lse, is_causal=False, sm_scale=None, impl="auto"):
-    """Returns ``(dq, dk, dv)`` with the shapes and dtypes of q, k, v."""
+    """Returns ``(dq, dk, dv)`` with the shapes and dtypes of q, k, v.  Strided do/q/k/v/out are read in place
+    where the tensor-core kernel applies; the gradients then take the layouts of q, k and v."""
     B, H_q, H_kv, S_q, S_k, D = validate_attention_layout(q, k, v)
     dt = _check_device_dtype(q, k, v, do, out)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
-    do, q, k, v, out = (t.contiguous() for t in (do, q, k, v, out))
     lse = lse.contiguous()
     if lse.dtype != torch.float32 or tuple(lse.shape) != (B, H_q, S_q):
         raise ValueError(f"lse must be float32 of shape {(B, H_q, S_q)}, got {lse.dtype} {tuple(lse.shape)}")
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if do.shape != q.shape or out.shape != q.shape:
+        raise ValueError(f"do and out must have q's shape {tuple(q.shape)}, got {tuple(do.shape)} and {tuple(out.shape)}")
     lib = _lib.load()
     impl_id = _lib.IMPL_BY_NAME[impl]
     ws_bytes = lib.skb_attn_bwd_workspace_bytes(B, H_q, H_kv, S_q, S_k, D, dt, impl_id)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    ins = (do, q, k, v, out)
+    if not all(t.is_contiguous() for t in ins) and all(_addressable(t) for t in ins):
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)   # keep dense permuted layouts
+        if all(_addressable(t) for t in (dq, dk, dv)):
+            with torch.cuda.device(q.device):
+                rc = lib.skb_attn_bwd_strided(do.data_ptr(), _strides3(do), q.data_ptr(), _strides3(q), k.data_ptr(),
+                                              _strides3(k), v.data_ptr(), _strides3(v), out.data_ptr(), _strides3(out),
+                                              lse.data_ptr(), dq.data_ptr(), _strides3(dq), dk.data_ptr(), _strides3(dk),
+                                              dv.data_ptr(), _strides3(dv), B, H_q, H_kv, S_q, S_k, D, dt,
+                                              int(bool(is_causal)), float(sm_scale), impl_id, ws.data_ptr(), ws_bytes,
+                                              _stream(q))
+            if rc != _lib.SKB_ERR_UNSUPPORTED:
+                _raise_for_status(rc, "flash_attn_bwd")
+                return dq, dk, dv
+    do, q, k, v, out = (t.contiguous() for t in ins)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     with torch.cuda.device(q.device):
         rc = lib.skb_attn_bwd(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                               dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H_q, H_kv, S_q, S_k, D, dt,
@@ -109,20 +170,21 @@ def flash_attn_bwd(do, q, k, v, out, lse, is_causal=False, sm_scale=None, impl="
 
 def flash_decode(q, k, v, sm_scale=None, cache_seqlens=None, return_lse=False, num_splits=0, impl="auto"):
     """Split-KV decode for ``q_len == 1``.  ``cache_seqlens`` (int32, ``(B,)``) limits sequence b to
-    its first ``cache_seqlens[b]`` cache rows; None attends to the whole cache (reference behaviour)."""
+    its first ``cache_seqlens[b]`` cache rows; None attends to the whole cache (reference behaviour).
+    Strided q and caches (e.g. a ``(B,S,H_kv,D)`` cache seen through ``transpose(1, 2)``) are read in place
+    where the group kernels apply."""
     B, H_q, H_kv, S_q, S_k, D = validate_attention_layout(q, k, v)
     assert S_q == 1, f"flash_decode requires q_len == 1, got {S_q}"
     dt = _check_device_dtype(q, k, v)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     lens_ptr = None
     if cache_seqlens is not None:
         if cache_seqlens.ndim != 1 or cache_seqlens.shape[0] != B:
             raise ValueError(f"cache_seqlens must have shape ({B},), got {tuple(cache_seqlens.shape)}")
         cache_seqlens = cache_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
         lens_ptr = cache_seqlens.data_ptr()
-    out = torch.empty_like(q)
+    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lse = torch.empty((B, H_q, 1), dtype=torch.float32, device=q.device)
     lib = _lib.load()
     impl_id = _lib.IMPL_BY_NAME[impl]
@@ -131,6 +193,16 @@ def flash_decode(q, k, v, sm_scale=None, cache_seqlens=None, return_lse=False, n
         num_splits = lib.skb_decode_num_splits(B, H_q, H_kv, S_k, D, dt, sms)
     ws_bytes = lib.skb_decode_workspace_bytes(B, H_q, H_kv, S_k, D, dt, num_splits)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    if not all(t.is_contiguous() for t in (q, k, v)) and all(_addressable(t) for t in (q, k, v)):
+        with torch.cuda.device(q.device):
+            rc = lib.skb_decode_strided(q.data_ptr(), _strides3(q), k.data_ptr(), _strides3(k), v.data_ptr(),
+                                        _strides3(v), lens_ptr, out.data_ptr(), _strides3(out), lse.data_ptr(),
+                                        B, H_q, H_kv, S_k, D, dt, float(sm_scale), int(num_splits), impl_id,
+                                        ws.data_ptr(), ws_bytes, _stream(q))
+        if rc != _lib.SKB_ERR_UNSUPPORTED:
+            _raise_for_status(rc, "flash_decode")
+            return (out, lse) if return_lse else out
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     with torch.cuda.device(q.device):
         rc = lib.skb_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), lens_ptr, out.data_ptr(), lse.data_ptr(),
                             B, H_q, H_kv, S_k, D, dt, float(sm_scale), int(num_splits), impl_id,

@@ -1,0 +1,122 @@
+"""Strided (view) inputs: the tensor-core kernels read (B,S,H,D)-layout tensors in place through their strides
+instead of the ``.contiguous()`` copies the reference makes (src/stackkernels/torch/attention.py:38-40,66).
+Results must equal those of the same call on contiguous copies bit for bit (same kernel, same arithmetic) and
+meet the parity bar against the oracle."""
+import pytest
+import torch
+
+from _parity import assert_parity
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def skb():
+    import stackkernels_b200 as m
+    return m
+
+
+def _bshd(B, S, H, D, dt, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(B, S, H, D, generator=g).to(dt)
+
+
+@pytest.mark.parametrize("dtype,D,Hq,Hkv,Sq,Sk,causal", [
+    ("bf16", 128, 4, 2, 300, 300, True),
+    ("fp16", 64, 4, 4, 256, 384, False),
+    ("bf16", 96, 6, 2, 200, 200, True),
+])
+def test_forward_backward_on_transposed_views(skb, dtype, D, Hq, Hkv, Sq, Sk, causal):
+    from _cases import DT
+    from oracle import attention_oracle as orc
+    from stackkernels_b200.launchers import flash_attn_bwd, flash_attn_fwd
+    dt = DT[dtype]
+    B = 2
+    xq, xk, xv, xdo = (_bshd(B, s, h, D, dt, i).cuda() for i, (s, h) in
+                       enumerate(((Sq, Hq), (Sk, Hkv), (Sk, Hkv), (Sq, Hq))))
+    q, k, v, do = (t.transpose(1, 2) for t in (xq, xk, xv, xdo))          # (B,H,S,D) views, not contiguous
+    assert not q.is_contiguous()
+    o, lse = flash_attn_fwd(q, k, v, is_causal=causal)
+    oc, lsec = flash_attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), is_causal=causal)
+    assert o.is_contiguous() and torch.equal(o, oc) and torch.equal(lse, lsec)
+    # result written straight into a (B,S,H,D) buffer
+    o_bshd = torch.empty_like(xq)
+    o2, _ = flash_attn_fwd(q, k, v, is_causal=causal, out=o_bshd.transpose(1, 2))
+    assert o2.data_ptr() == o_bshd.data_ptr() and torch.equal(o_bshd.transpose(1, 2), oc)
+    eo, el = orc.attention_forward(q.cpu(), k.cpu(), v.cpu(), causal=causal)
+    assert_parity(o, eo, dtype, "strided O")
+    assert_parity(lse, el, dtype, "strided LSE")
+
+    dq, dk, dv = flash_attn_bwd(do, q, k, v, o2, lse, is_causal=causal)
+    dqc, dkc, dvc = flash_attn_bwd(do.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(), oc, lsec,
+                                   is_causal=causal)
+    assert dq.stride() == q.stride() and dk.stride() == k.stride()         # gradients keep the inputs' layout
+    assert torch.equal(dk, dkc) and torch.equal(dv, dvc)
+    edq, edk, edv = orc.attention_backward(do.cpu(), q.cpu(), k.cpu(), v.cpu(), causal=causal)
+    assert_parity(dq, edq, dtype, "strided dQ")                            # dQ: fp32 atomics, order-dependent
+    assert_parity(dk, edk, dtype, "strided dK")
+    assert_parity(dv, edv, dtype, "strided dV")
+    assert skb._lib.device_status() == 0
+
+
+def test_autograd_on_packed_qkv(skb):
+    """q, k, v sliced out of one packed (B,S,3,H,D) projection and transposed, through the public API."""
+    from oracle import attention_oracle as orc
+    B, S, H, D = 2, 256, 4, 128
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, S, 3, H, D, generator=g).bfloat16().cuda().requires_grad_(True)
+    q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+    out = skb.flash_attention(q, k, v, is_causal=True)
+    g2 = torch.Generator().manual_seed(6)
+    do = torch.randn(B, H, S, D, generator=g2).bfloat16().cuda()
+    out.backward(do)
+    torch.cuda.synchronize()
+    qc, kc, vc = (qkv.detach()[:, :, i].transpose(1, 2).contiguous().cpu() for i in range(3))
+    eo, _ = orc.attention_forward(qc, kc, vc, causal=True)
+    edq, edk, edv = orc.attention_backward(do.cpu(), qc, kc, vc, causal=True)
+    assert_parity(out, eo, "bf16", "packed O")
+    grad = qkv.grad
+    for i, (e, n) in enumerate(((edq, "dQ"), (edk, "dK"), (edv, "dV"))):
+        assert_parity(grad[:, :, i].transpose(1, 2), e, "bf16", f"packed {n}")
+    assert skb._lib.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype,D,Hq,Hkv", [("bf16", 128, 8, 2), ("fp16", 128, 64, 2), ("bf16", 96, 48, 2),
+                                            ("fp16", 64, 4, 4)])
+def test_decode_on_bshd_cache(skb, dtype, D, Hq, Hkv):
+    """KV cache stored (B,S,H_kv,D) and viewed as (B,H_kv,S,D); q a view of a (B,1,H_q,D) projection."""
+    from _cases import DT
+    from oracle import attention_oracle as orc
+    from stackkernels_b200.launchers import flash_decode
+    dt = DT[dtype]
+    B, cap = 3, 1500
+    kc, vc = (_bshd(B, cap, Hkv, D, dt, i).cuda().transpose(1, 2) for i in (1, 2))
+    q = _bshd(B, 1, Hq, D, dt, 3).cuda().transpose(1, 2)
+    lens = torch.tensor([1500, 1, 777], dtype=torch.int32)
+    assert not kc.is_contiguous()
+    o, lse = flash_decode(q, kc, vc, cache_seqlens=lens.cuda(), return_lse=True)
+    oc, lsec = flash_decode(q.contiguous(), kc.contiguous(), vc.contiguous(), cache_seqlens=lens.cuda(),
+                            return_lse=True)
+    assert torch.equal(o, oc) and torch.equal(lse, lsec)
+    eo, el = orc.decode_forward(q.cpu(), kc.cpu(), vc.cpu(), cache_seqlens=lens)
+    assert_parity(o, eo, dtype, "strided decode O")
+    assert_parity(lse, el, dtype, "strided decode LSE")
+    assert skb._lib.device_status() == 0
+
+
+def test_views_the_kernels_cannot_address_are_copied(skb):
+    """fp32 views, odd strides and misaligned bases take the reference's route (a contiguous copy)."""
+    from oracle import attention_oracle as orc
+    from stackkernels_b200.launchers import flash_attn_fwd
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(1, 160, 2, 64, generator=g).cuda()                       # fp32 transposed view
+    q = x.transpose(1, 2)
+    o, _ = flash_attn_fwd(q, q, q, is_causal=True)
+    eo, _ = orc.attention_forward(q.cpu(), q.cpu(), q.cpu(), causal=True)
+    assert_parity(o, eo, "fp32", "fp32 view")
+    y = torch.randn(1, 2, 160, 68, generator=g).bfloat16().cuda()[..., 4:]   # base 8 bytes off, row stride 68
+    assert y.data_ptr() % 16 != 0
+    o, _ = flash_attn_fwd(y, y, y, is_causal=False)
+    eo, _ = orc.attention_forward(y.cpu(), y.cpu(), y.cpu(), causal=False)
+    assert_parity(o, eo, "bf16", "misaligned view")
+    assert skb._lib.device_status() == 0
