@@ -52,7 +52,7 @@ NCU_TRAFFIC_BYTES = {
     "bwd_profile": 1136.6e6,
     "decode_c4": 8 * 855.5e6,             # profiles/decode_group_bf16_d128.md
     "decode_profile": 855.5e6,
-    "decode_c5": 1.0757e9,
+    "decode_c5": 1.0830e9,               # profiles/decode_tc_fp16_d128.md (read 1.0741 GB + write 8.9 MB)
 }
 
 
