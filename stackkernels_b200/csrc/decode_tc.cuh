@@ -1,15 +1,21 @@
-// Split-KV decode on tcgen05 tensor cores for wide GQA/MQA groups (16-bit, head dim 128, group <= 128).
+// One-tile attention on tcgen05 tensor cores: split-KV decode for wide GQA/MQA groups, and prefill forward for
+// head dimensions the two-tile kernel of fwd_sm100.cuh has no tensor memory for (16-bit, tiles of 128 or 256
+// columns).
 //
-// With G query heads per KV head the decode step needs G FLOP per KV byte; at G = 64 that is more than
-// warp-level mma.sync and its ldmatrix traffic sustain (decode_group.cuh becomes compute bound), so this
-// kernel puts the group's heads on the M dimension of 128-row tcgen05 MMAs (rows >= G are don't-care):
-//   S[buf] = Q K_j^T  (Q and K from shared memory)      O += P_j V_j  (P from TMEM, V from shared memory)
-// One CTA = (split, kv head, batch).  Warp 0 streams 128-row K/V tiles with TMA through a 3-stage ring,
-// warp 1 owns TMEM and issues the MMAs (S of the next tile is queued before PV of the current one: S is
-// double buffered), warps 4-7 run the same fp32 online softmax as the prefill kernel, one head per thread.
-// V rows past the sequence end are zeroed in shared memory before PV (stale cache rows may hold NaNs).
-// Partials (unnormalised O, max, sum) use the layout of decode_combine_kernel.
-// TMEM columns: S[0] [0,128) S[1] [128,256) O [256,384).
+// Decode (PREFILL = false).  With G query heads per KV head the decode step needs G FLOP per KV byte; at G = 64
+// that is more than warp-level mma.sync and its ldmatrix traffic sustain (decode_group.cuh becomes compute
+// bound), so this kernel puts the group's heads on the M dimension of 128-row tcgen05 MMAs (rows >= G are
+// don't-care).  One CTA = (split, kv head, batch); partials (unnormalised O, max, sum) use the layout of
+// decode_combine_kernel.  V rows past the sequence end are zeroed in shared memory before PV (stale cache rows
+// may hold NaNs).
+// Prefill (PREFILL = true).  One CTA = 128 query rows of one (batch, q head); rows are query positions, the
+// bottom-right causal mask limits each row to a prefix of the keys, O is normalised and stored with LSE.
+//
+// Both:  S[buf] = Q K_j^T  (Q and K from shared memory)      O += P_j V_j  (P from TMEM, V from shared memory)
+// Warp 0 streams K/V tiles with TMA through a ring (HD = 128: 128-row tiles, 3 stages; HD = 256: 64-row tiles,
+// 2 stages), warp 1 owns TMEM and issues the MMAs (S of the next tile is queued before PV of the current one:
+// S is double buffered), warps 4-7 run the fp32 online softmax of the prefill kernel, one row per thread.
+// TMEM columns: S[0] [0,128) S[1] [128,256) O [256, 256+HD).
 #pragma once
 #include "fwd_sm100.cuh"
 
@@ -21,8 +27,15 @@ using sm100::kBoxBytes;
 using sm100::pack2;
 
 constexpr int kThreads = 256;
-constexpr int kStages = 3;
-constexpr int kTile = 2 * kBoxBytes;     // 128 x 128 16-bit tile = 32 KB
+
+template <int HD> struct Cfg {
+  static constexpr int kKvRows = HD == 128 ? 128 : 64;          // KV rows per tile
+  static constexpr int kStages = HD == 128 ? 3 : 2;
+  static constexpr int kQBytes = 128 * HD * 2;                  // Q tile: 128 rows
+  static constexpr int kKvBytes = kKvRows * HD * 2;             // one K or V tile
+  static constexpr int kKvBox = kKvRows * 128;                  // one 64-column box of a K/V tile
+  static constexpr int kSmemBytes = 1024 + kQBytes + 2 * kStages * kKvBytes + 256;
+};
 
 enum Bar {
   Q_FULL = 0,
@@ -36,38 +49,66 @@ enum Bar {
   DRAIN = 18,
   NUM = 19
 };
-constexpr int kSmemBytes = 1024 + (1 + 2 * kStages) * kTile + 256;
 
-template <typename T>
+// Arguments that differ between the two uses of the kernel.
+struct DecodeArgs {            // PREFILL = false
+  const int32_t* seqlens;      // (B,) or null
+  float* part_o;               // (B, Hq, nsplit, D) fp32
+  float2* part_ml;             // (B, Hq, nsplit) (max, sum), max in the log2 domain
+  int nsplit;
+};
+template <typename T> struct PrefillArgs {   // PREFILL = true
+  T* o;
+  Strides o_str;
+  float* lse;                  // (B, Hq, Sq)
+  int Sq, causal;
+};
+
+// Sk: rows of the K/V tensors (decode: cache capacity).  D <= HD (a multiple of 8) is the head dimension in
+// memory; the bulk copies zero columns [D, HD).
+template <typename T, int HD, bool PREFILL>
 __global__ void __launch_bounds__(kThreads, 1)
-decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-              const __grid_constant__ CUtensorMap tm_v, const int32_t* __restrict__ seqlens,
-              float* __restrict__ part_o, float2* __restrict__ part_ml, int Hq, int Hkv, int Scap, int D, int nsplit,
-              float scale_log2) {
-  // D <= 128 (a multiple of 8) is the head dimension in memory; the bulk copies zero columns [D, 128).
-  constexpr uint32_t IDESC_QK = ptx::idesc_f16(Fmt<T>::v, 128, 128, 0, 0);
-  constexpr uint32_t IDESC_PV = ptx::idesc_f16(Fmt<T>::v, 128, 128, 0, 1);
+tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+            const __grid_constant__ CUtensorMap tm_v, const DecodeArgs dec, const PrefillArgs<T> pre, int Hq, int Hkv,
+            int Sk, int D, float scale_log2) {
+  using C = Cfg<HD>;
+  constexpr int KV = C::kKvRows, STAGES = C::kStages;
+  constexpr uint32_t IDESC_QK = ptx::idesc_f16(Fmt<T>::v, 128, KV, 0, 0);
+  constexpr uint32_t IDESC_PV = ptx::idesc_f16(Fmt<T>::v, 128, HD, 0, 1);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (sbase - ptx::smem_u32(smem_raw));
   const uint32_t sQ = sbase;
-  auto sK = [&](int st) -> uint32_t { return sbase + kTile + (uint32_t)st * 2u * kTile; };
-  auto sV = [&](int st) -> uint32_t { return sbase + 2 * kTile + (uint32_t)st * 2u * kTile; };
-  const uint32_t sBar = sbase + (1 + 2 * kStages) * kTile;
+  auto sK = [&](int st) -> uint32_t { return sbase + C::kQBytes + (uint32_t)st * 2u * C::kKvBytes; };
+  auto sV = [&](int st) -> uint32_t { return sK(st) + C::kKvBytes; };
+  const uint32_t sBar = sbase + C::kQBytes + 2 * STAGES * C::kKvBytes;
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gbase + (sBar - sbase) + NUM * 8);
   volatile int* s_abort = reinterpret_cast<volatile int*>(gbase + (sBar - sbase) + NUM * 8 + 8);
   auto bar = [&](int i) -> uint32_t { return sBar + 8u * (uint32_t)i; };
 
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
-  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int G = Hq / Hkv;
-  const int len = seqlens ? min(max(seqlens[b], 0), Scap) : Scap;
-  const int chunk = cdiv(cdiv(len, nsplit), 128) * 128;
-  const int start = split * chunk;
-  const int end = min(len, start + chunk);
-  const int nt = end > start ? cdiv(end - start, 128) : 0;
+  const int b = blockIdx.z;
+  // decode: blockIdx = (split, kv head, batch); prefill: (query tile, q head, batch), heaviest tiles first
+  const int split = PREFILL ? 0 : blockIdx.x;
+  const int hq = PREFILL ? blockIdx.y : 0;
+  const int hkv = PREFILL ? hq / G : blockIdx.y;
+  const int qtile = PREFILL ? (pre.causal ? gridDim.x - 1 - blockIdx.x : blockIdx.x) : 0;
+  const int q0 = qtile * 128;
+  const int shift = PREFILL ? Sk - pre.Sq : 0;                 // bottom-right causal alignment
+  int start, end;
+  if (PREFILL) {
+    start = 0;
+    end = pre.causal ? max(0, min(Sk, q0 + 128 + shift)) : Sk;
+  } else {
+    const int len = dec.seqlens ? min(max(dec.seqlens[b], 0), Sk) : Sk;
+    const int chunk = cdiv(cdiv(len, dec.nsplit), KV) * KV;
+    start = split * chunk;
+    end = min(len, start + chunk);
+  }
+  const int nt = end > start ? cdiv(end - start, KV) : 0;
 
   if (threadIdx.x == 0) {
     *s_abort = 0;
@@ -89,22 +130,28 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if (lane == 0 && nt > 0) {
       // ------------------------------------------------------------------ TMA producer
       ptx::prefetch_tmap(&tm_q); ptx::prefetch_tmap(&tm_k); ptx::prefetch_tmap(&tm_v);
-      ptx::mbar_expect_tx(bar(Q_FULL), kTile);
-      // rows = query heads of this group (q viewed as {D, Hq, B}); rows >= G are other heads or zero fill
-      for (int h = 0; h < 2; ++h) ptx::tma_load_3d(sQ + h * kBoxBytes, &tm_q, h * 64, hkv * G, b, bar(Q_FULL));
+      ptx::mbar_expect_tx(bar(Q_FULL), C::kQBytes);
+      for (int h = 0; h < HD / 64; ++h) {
+        if (PREFILL)   // rows = query positions of head hq (q as {D, Sq, Hq, B})
+          ptx::tma_load_4d(sQ + h * kBoxBytes, &tm_q, h * 64, q0, hq, b, bar(Q_FULL));
+        else           // rows = query heads of this group (q as {D, Hq, B}); rows >= G: other heads or zero fill
+          ptx::tma_load_3d(sQ + h * kBoxBytes, &tm_q, h * 64, hkv * G, b, bar(Q_FULL));
+      }
       bool ok = true;
       for (int j = 0; j < nt && ok; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (uint32_t)((j / kStages) & 1) ^ 1u;
-        const int row = start + j * 128;
+        const int st = j % STAGES;
+        const uint32_t ph = (uint32_t)((j / STAGES) & 1) ^ 1u;
+        const int row = start + j * KV;
         ok = ptx::mbar_wait(bar(K_EMPTY + st), ph, s_abort);
         if (!ok) break;
-        ptx::mbar_expect_tx(bar(K_FULL + st), kTile);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sK(st) + h * kBoxBytes, &tm_k, h * 64, row, hkv, b, bar(K_FULL + st));
+        ptx::mbar_expect_tx(bar(K_FULL + st), C::kKvBytes);
+        for (int h = 0; h < HD / 64; ++h)
+          ptx::tma_load_4d(sK(st) + h * C::kKvBox, &tm_k, h * 64, row, hkv, b, bar(K_FULL + st));
         ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
         if (!ok) break;
-        ptx::mbar_expect_tx(bar(V_FULL + st), kTile);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sV(st) + h * kBoxBytes, &tm_v, h * 64, row, hkv, b, bar(V_FULL + st));
+        ptx::mbar_expect_tx(bar(V_FULL + st), C::kKvBytes);
+        for (int h = 0; h < HD / 64; ++h)
+          ptx::tma_load_4d(sV(st) + h * C::kKvBox, &tm_v, h * 64, row, hkv, b, bar(V_FULL + st));
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (13u << 16));
     }
@@ -113,15 +160,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const bool leader = ptx::elect_one();
     bool ok = true;
     auto issue_qk = [&](int j) {
-      const uint32_t k = sK(j % kStages);
+      const uint32_t k = sK(j % STAGES);
       if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * kBoxBytes + (uint32_t)(kk & 3) * 32u;
-          ptx::mma_ss(tS(j & 1), ptx::desc_sw128_kmajor(sQ + off), ptx::desc_sw128_kmajor(k + off), IDESC_QK, kk > 0);
+        for (int kk = 0; kk < HD / 16; ++kk) {      // K-major: 32 bytes per k-step, next 64-column box after 4
+          const uint32_t in_row = (uint32_t)(kk & 3) * 32u;
+          ptx::mma_ss(tS(j & 1), ptx::desc_sw128_kmajor(sQ + (uint32_t)(kk >> 2) * kBoxBytes + in_row),
+                      ptx::desc_sw128_kmajor(k + (uint32_t)(kk >> 2) * C::kKvBox + in_row), IDESC_QK, kk > 0);
         }
         ptx::mma_commit(bar(S_FULL + (j & 1)));
-        ptx::mma_commit(bar(K_EMPTY + j % kStages));
+        ptx::mma_commit(bar(K_EMPTY + j % STAGES));
       }
     };
     if (nt > 0) {
@@ -129,21 +177,22 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (ok) { ptx::tc_fence_after(); issue_qk(0); }
     }
     for (int j = 0; j < nt && ok; ++j) {
-      const int st = j % kStages, buf = j & 1;
+      const int st = j % STAGES, buf = j & 1;
       if (j + 1 < nt) {
-        ok = ptx::mbar_wait_warp(bar(K_FULL + (j + 1) % kStages), (uint32_t)((j + 1) / kStages) & 1u, s_abort);
+        ok = ptx::mbar_wait_warp(bar(K_FULL + (j + 1) % STAGES), (uint32_t)((j + 1) / STAGES) & 1u, s_abort);
         if (!ok) break;
         ptx::tc_fence_after();
         issue_qk(j + 1);
       }
-      ok = ptx::mbar_wait_warp(bar(V_FULL + st), (uint32_t)(j / kStages) & 1u, s_abort) &&
+      ok = ptx::mbar_wait_warp(bar(V_FULL + st), (uint32_t)(j / STAGES) & 1u, s_abort) &&
            ptx::mbar_wait_warp(bar(P_FULL + buf), (uint32_t)(j >> 1) & 1u, s_abort);
       if (!ok) break;
       ptx::tc_fence_after();
       if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          ptx::mma_ts(tO, tS(buf) + kk * 8, ptx::desc_sw128_mnmajor(sV(st) + kk * 2048, kBoxBytes), IDESC_PV, (j > 0) || (kk > 0));
+        for (int kk = 0; kk < KV / 16; ++kk)        // MN-major V: 16 rows (2048 bytes) per k-step, boxes kKvBox apart
+          ptx::mma_ts(tO, tS(buf) + kk * 8, ptx::desc_sw128_mnmajor(sV(st) + kk * 2048, C::kKvBox), IDESC_PV,
+                      (j > 0) || (kk > 0));
         ptx::mma_commit(bar(V_EMPTY + st));
         ptx::mma_commit(bar(O_READY));
       }
@@ -152,42 +201,49 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if (!ptx::mbar_wait_warp(bar(DRAIN), 0, s_abort)) ok = false;
     if (!ok && leader) atomicCAS(&g_dev_status, 0u, (14u << 16));
   } else if (warp >= 4) {
-    // -------------------------------------------------------------------- softmax: one query head per thread
+    // -------------------------------------------------------------------- softmax: one row per thread
     const int wq = warp & 3;
-    const int r = wq * 32 + lane;                  // head within the group = TMEM lane
+    const int r = wq * 32 + lane;                  // row of the tile = TMEM lane (decode: head within the group)
     const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
+    // prefill: last key this row may see (bottom-right causal alignment); decode rows all see the whole tile
+    const int row_limit = PREFILL ? (pre.causal ? min(Sk - 1, q0 + r + shift) : Sk - 1) : 0;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nt; ++j) {
-      const int buf = j & 1, st = j % kStages;
+      const int buf = j & 1, st = j % STAGES;
       ok = ptx::mbar_wait_warp(bar(S_FULL + buf), (uint32_t)(j >> 1) & 1u, s_abort);
       if (!ok) break;
       ptx::tc_fence_after();
-      uint32_t sr[128];
+      uint32_t sr[KV];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) ptx::tmem_ld32(tS(buf) + t_lane + c * 32, sr + c * 32);
+      for (int c = 0; c < KV / 32; ++c) ptx::tmem_ld32(tS(buf) + t_lane + c * 32, sr + c * 32);
       ptx::tmem_wait_ld();
-      const int valid = end - (start + j * 128);   // rows of this tile inside the sequence (>= 1)
-      if (valid < 128) {
+      // columns [0, valid) of this tile are visible to this row
+      const int tile_rows = end - (start + j * KV);                       // rows of the tile inside the sequence
+      const int valid = PREFILL ? max(0, min(KV, row_limit - j * KV + 1)) : min(KV, tile_rows);
+      if (valid < KV) {
 #pragma unroll
-        for (int c = 0; c < 128; ++c)
+        for (int c = 0; c < KV; ++c)
           if (c >= valid) sr[c] = 0xff800000u;     // -inf
-        // clear the V rows past the end (each thread clears whole rows r' = its lane index)
-        ok = ptx::mbar_wait_warp(bar(V_FULL + st), (uint32_t)(j / kStages) & 1u, s_abort);
+      }
+      if (!PREFILL && tile_rows < KV) {
+        // decode: clear the V rows past the end of the sequence -- stale cache rows may hold NaNs (a prefill tile
+        // past the end of K/V is zero-filled by the bulk copy).  Thread r clears row r.
+        ok = ptx::mbar_wait_warp(bar(V_FULL + st), (uint32_t)(j / STAGES) & 1u, s_abort);
         if (!ok) break;
-        if (r >= valid) {
+        if (r >= tile_rows && r < KV) {
           uint8_t* vrow = gbase + (sV(st) - sbase) + r * 128;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            *reinterpret_cast<uint4*>(vrow + c * 16) = make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(vrow + kBoxBytes + c * 16) = make_uint4(0u, 0u, 0u, 0u);
-          }
+          for (int h = 0; h < HD / 64; ++h)
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              *reinterpret_cast<uint4*>(vrow + h * C::kKvBox + c * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 128; c += 8) {
+      for (int c = 0; c < KV; c += 8) {
         mx0 = ptx::max3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
         mx1 = ptx::max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
         mx2 = ptx::max3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
@@ -205,7 +261,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const uint64_t sc2 = ptx::f2_pack(scale_log2, scale_log2), nm2 = ptx::f2_pack(-mref, -mref);
       uint64_t sumA = ptx::f2_pack(0.f, 0.f), sumB = sumA;
 #pragma unroll
-      for (int c = 0; c < 128; c += 8) {
+      for (int c = 0; c < KV; c += 8) {
         float x[8], pe[8];
 #pragma unroll
         for (int e = 0; e < 8; e += 2)
@@ -214,7 +270,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
         for (int e = 0; e < 6; ++e) pe[e] = ptx::ex2(x[e]);
         ptx::exp2_poly2(x[6], x[7], pe[6], pe[7]);
-        if (valid < 128) {                         // polynomial exponentials of -inf are tiny, not zero
+        if (valid < KV) {                          // polynomial exponentials of -inf are tiny, not zero
 #pragma unroll
           for (int e = 0; e < 8; ++e)
             if (c + e >= valid) pe[e] = 0.f;
@@ -230,14 +286,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::f2_unpack(sumB, b0, b1);
         l += (a0 + a1) + (b0 + b1);
       }
-      ptx::tmem_st32(tS(buf) + t_lane, sr);
-      ptx::tmem_st32(tS(buf) + t_lane + 32, sr + 32);
+#pragma unroll
+      for (int c = 0; c < KV / 64; ++c) ptx::tmem_st32(tS(buf) + t_lane + c * 32, sr + c * 32);
       if (j > 0 && __any_sync(0xffffffffu, grow_m)) {
-        ok = ptx::mbar_wait_warp(bar(O_READY), (uint32_t)(j - 1) & 1u, s_abort);   // PV of tile j-1 finished
+        // PV of tile j-1 finished?  (S_FULL of tile j implies PV of tile j-2 finished, so the barrier is at most
+        // one phase behind and the parity wait cannot return early.)
+        ok = ptx::mbar_wait_warp(bar(O_READY), (uint32_t)(j - 1) & 1u, s_abort);
         if (!ok) break;
         ptx::tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t orr[32];
           ptx::tmem_ld32(tO + t_lane + c * 32, orr);
           ptx::tmem_wait_ld();
@@ -250,34 +308,65 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(P_FULL + buf));
     }
-    // ------------------------------------------------------------------ partial results for the combine kernel
+    // ------------------------------------------------------------------ results
     // DRAIN completes once, after every MMA of the CTA. O_READY cannot be used here: with S double-buffered
     // this warp may be two tiles ahead of the last finished PV product, and a parity wait on a barrier that is
     // two phases behind returns at once.
     if (ok) ok = ptx::mbar_wait_warp(bar(DRAIN), 0, s_abort);
     if (ok) {
       ptx::tc_fence_after();
-      const size_t pbase = ((size_t)b * Hq + (size_t)hkv * G + min(r, G - 1)) * nsplit + split;
       const bool seen = (m != -INFINITY) && l > 0.f;
+      if (PREFILL) {
+        const int grow = q0 + r;
+        const float inv = seen ? 1.f / l : 0.f;
+        T* orow = pre.o + pre.o_str.at(b, hq, min(grow, pre.Sq - 1));
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t orr[32];
-        if (nt > 0) {
-          ptx::tmem_ld32(tO + t_lane + c * 32, orr);
-          ptx::tmem_wait_ld();
-        } else {
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t orr[32];
+          if (nt > 0) {
+            ptx::tmem_ld32(tO + t_lane + c * 32, orr);
+            ptx::tmem_wait_ld();
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) orr[i] = 0u;
+            for (int i = 0; i < 32; ++i) orr[i] = 0u;
+          }
+          if (grow < pre.Sq) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (c * 32 + i >= D) break;
+              uint4 w;
+              w.x = pack2(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv, T());
+              w.y = pack2(__uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv, T());
+              w.z = pack2(__uint_as_float(orr[i + 4]) * inv, __uint_as_float(orr[i + 5]) * inv, T());
+              w.w = pack2(__uint_as_float(orr[i + 6]) * inv, __uint_as_float(orr[i + 7]) * inv, T());
+              *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+            }
+          }
         }
-        if (r < G) {
+        if (grow < pre.Sq) pre.lse[((size_t)b * Hq + hq) * pre.Sq + grow] = seen ? (m + log2f(l)) * kLn2 : -INFINITY;
+      } else {
+        // partial results for the combine kernel
+        const size_t pbase = ((size_t)b * Hq + (size_t)hkv * G + min(r, G - 1)) * dec.nsplit + split;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            if (c * 32 + i < D)
-              *reinterpret_cast<uint4*>(part_o + pbase * D + c * 32 + i) =
-                seen ? make_uint4(orr[i], orr[i + 1], orr[i + 2], orr[i + 3]) : make_uint4(0u, 0u, 0u, 0u);
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t orr[32];
+          if (nt > 0) {
+            ptx::tmem_ld32(tO + t_lane + c * 32, orr);
+            ptx::tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orr[i] = 0u;
+          }
+          if (r < G) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              if (c * 32 + i < D)
+                *reinterpret_cast<uint4*>(dec.part_o + pbase * D + c * 32 + i) =
+                    seen ? make_uint4(orr[i], orr[i + 1], orr[i + 2], orr[i + 3]) : make_uint4(0u, 0u, 0u, 0u);
+          }
         }
+        if (r < G) dec.part_ml[pbase] = seen ? make_float2(m, l) : make_float2(-INFINITY, 0.f);
       }
-      if (r < G) part_ml[pbase] = seen ? make_float2(m, l) : make_float2(-INFINITY, 0.f);
     } else if (lane == 0) {
       atomicCAS(&g_dev_status, 0u, (15u << 16) | (unsigned)warp);
     }

@@ -204,9 +204,9 @@ bool strides_ok(const void* p, const Strides& s, int B, int H, int S) {
 }
 
 bool fwd_sm100_covers(int D, int dtype, float scale) {
-  // any D <= 128 (a multiple of 8): the kernels are built for 64 and 128 columns and D is zero-padded
-  // up to the next of the two by the bulk copies
-  return (dtype == SKB_F16 || dtype == SKB_BF16) && D <= 128 && D % 8 == 0 && scale > 0.f;
+  // any D <= 256 (a multiple of 8): the kernels are built for 64, 128 and 256 columns and D is zero-padded
+  // up to the next of them by the bulk copies
+  return (dtype == SKB_F16 || dtype == SKB_BF16) && D <= 256 && D % 8 == 0 && scale > 0.f;
 }
 
 template <typename T, int HD>
@@ -223,6 +223,28 @@ int launch_fwd_sm100(const void* q, const Strides& qs, const void* k, const Stri
   if (int rc = set_smem(kern, smem)) return rc;
   dim3 grid(cdiv(Sq, 2 * sm100::kTileM), Hq, B);
   kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, os, lse, Hq, Hkv, Sq, Sk, D, causal, scale * kLog2e);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
+// 128 < D <= 256: one 128-row query tile per CTA (decode_tc.cuh); the two-tile kernel has no tensor memory for
+// two 256-column accumulators.
+template <typename T>
+int launch_fwd_tile256(const void* q, const Strides& qs, const void* k, const Strides& ks, const void* v,
+                       const Strides& vs, void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Sq, int Sk,
+                       int D, int causal, float scale, cudaStream_t st) {
+  using C = dtc::Cfg<256>;
+  CUtensorMap mq, mk, mv;
+  const int dt = DtypeOf<T>::value;
+  if (int rc = make_map_4d(&mq, dt, q, D, Sq, Hq, B, qs)) return rc;
+  if (int rc = make_map_4d(&mk, dt, k, D, Sk, Hkv, B, ks, C::kKvRows)) return rc;
+  if (int rc = make_map_4d(&mv, dt, v, D, Sk, Hkv, B, vs, C::kKvRows)) return rc;
+  auto kern = dtc::tile_kernel<T, 256, true>;
+  if (int rc = set_smem(kern, C::kSmemBytes)) return rc;
+  const dtc::DecodeArgs dec{nullptr, nullptr, nullptr, 1};
+  const dtc::PrefillArgs<T> pre{(T*)o, os, lse, Sq, causal};
+  kern<<<dim3(cdiv(Sq, 128), Hq, B), dtc::kThreads, C::kSmemBytes, st>>>(mq, mk, mv, dec, pre, Hq, Hkv, Sk, D,
+                                                                        scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -305,12 +327,14 @@ int launch_bwd_sm100(const BwdTensors& t, const float* lse, int B, int Hq, int H
 
 // ------------------------------------------------------------------------------------ group decode
 bool decode_group_covers(int Hq, int Hkv, int D, int dtype) {
-  return (dtype == SKB_F16 || dtype == SKB_BF16) && D <= 128 && D % 8 == 0 && Hq / Hkv <= 64;
+  const int G = Hq / Hkv;
+  return (dtype == SKB_F16 || dtype == SKB_BF16) && D % 8 == 0 && ((D <= 64 && G <= 64) || (D > 64 && D <= 256 && G <= 128));
 }
-// Within the group path: more than 16 query heads per KV head at 64 < D <= 128 run on tcgen05
-// (decode_tc.cuh), narrower groups and D <= 64 on the mma.sync kernel (decode_group.cuh).  Both kernels
-// are built for 64- or 128-column tiles; other D are zero-padded by the bulk copies.
-bool decode_uses_tcgen05(int Hq, int Hkv, int D) { return D > 64 && D <= 128 && Hq / Hkv > 16; }
+// Within the group path: D <= 64, and groups of up to 16 heads at D <= 128, run on the mma.sync kernel
+// (decode_group.cuh, two CTAs per SM); wider groups (up to 128 heads) and 128 < D <= 256 run on tcgen05
+// (decode_tc.cuh).  The kernels are built for 64-, 128- or 256-column tiles; other D are zero-padded by the
+// bulk copies.
+bool decode_uses_tcgen05(int Hq, int Hkv, int D) { return D > 128 || (D > 64 && Hq / Hkv > 16); }
 
 template <typename T, int HD, int MT>
 int launch_decode_group(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const Strides& qs,
@@ -325,6 +349,27 @@ int launch_decode_group(const CUtensorMap& mk, const CUtensorMap& mv, const void
   return SKB_OK;
 }
 
+template <typename T, int HD>
+int launch_decode_tile(const void* q, const Strides& qs, const void* kc, const Strides& ks, const void* vc,
+                       const Strides& vs, const int32_t* lens, void* o, const Strides& os, float* lse, int B, int Hq,
+                       int Hkv, int Scap, int D, int nsplit, float scale, float* part_o, float2* part_ml, cudaStream_t st) {
+  using C = dtc::Cfg<HD>;
+  const int dt = DtypeOf<T>::value;
+  CUtensorMap mq, mk, mv;
+  if (int rc = make_map_q_heads(&mq, dt, q, D, Hq, B, qs)) return rc;
+  if (int rc = make_map_4d(&mk, dt, kc, D, Scap, Hkv, B, ks, C::kKvRows)) return rc;
+  if (int rc = make_map_4d(&mv, dt, vc, D, Scap, Hkv, B, vs, C::kKvRows)) return rc;
+  auto kern = dtc::tile_kernel<T, HD, false>;
+  if (int rc = set_smem(kern, C::kSmemBytes)) return rc;
+  const dtc::DecodeArgs dec{lens, part_o, part_ml, nsplit};
+  const dtc::PrefillArgs<T> pre{nullptr, Strides{0, 0, 0}, nullptr, 1, 0};
+  kern<<<dim3(nsplit, Hkv, B), dtc::kThreads, C::kSmemBytes, st>>>(mq, mk, mv, dec, pre, Hq, Hkv, Scap, D, scale * kLog2e);
+  SKB_CUDA(cudaGetLastError());
+  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, os, lse, Hq, D, nsplit);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
 template <typename T>
 int decode_group(const void* q, const Strides& qs, const void* kc, const Strides& ks, const void* vc, const Strides& vs,
                  const int32_t* lens, void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Scap, int D,
@@ -333,19 +378,9 @@ int decode_group(const void* q, const Strides& qs, const void* kc, const Strides
   const int G = Hq / Hkv;
   int rc;
   if (decode_uses_tcgen05(Hq, Hkv, D)) {
-    // wide groups: tcgen05 kernel with the group's heads as the MMA M dimension (decode_tc.cuh)
-    CUtensorMap mq, mk128, mv128;
-    if (int r2 = make_map_q_heads(&mq, dt, q, D, Hq, B, qs)) return r2;
-    if (int r2 = make_map_4d(&mk128, dt, kc, D, Scap, Hkv, B, ks)) return r2;
-    if (int r2 = make_map_4d(&mv128, dt, vc, D, Scap, Hkv, B, vs)) return r2;
-    auto kern = dtc::decode_kernel<T>;
-    if (int r2 = set_smem(kern, dtc::kSmemBytes)) return r2;
-    kern<<<dim3(nsplit, Hkv, B), dtc::kThreads, dtc::kSmemBytes, st>>>(mq, mk128, mv128, lens, part_o, part_ml, Hq, Hkv,
-                                                                      Scap, D, nsplit, scale * kLog2e);
-    SKB_CUDA(cudaGetLastError());
-    general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, os, lse, Hq, D, nsplit);
-    SKB_CUDA(cudaGetLastError());
-    return SKB_OK;
+    // wide groups / wide heads: tcgen05 kernel with the group's heads as the MMA M dimension (decode_tc.cuh)
+    return D > 128 ? launch_decode_tile<T, 256>(q, qs, kc, ks, vc, vs, lens, o, os, lse, B, Hq, Hkv, Scap, D, nsplit, scale, part_o, part_ml, st)
+                   : launch_decode_tile<T, 128>(q, qs, kc, ks, vc, vs, lens, o, os, lse, B, Hq, Hkv, Scap, D, nsplit, scale, part_o, part_ml, st);
   }
   CUtensorMap mk, mv;
   if (int r2 = make_map_4d(&mk, dt, kc, D, Scap, Hkv, B, ks, dgrp::kTileN)) return r2;
@@ -451,6 +486,11 @@ int attn_fwd_impl(const void* q, const Strides& qs, const void* k, const Strides
   }
   if (use_tc) {
 #define SKB_FWD(T_, HD_) launch_fwd_sm100<T_, HD_>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st)
+    if (D > 128) {
+      if (dtype == SKB_F16)
+        return launch_fwd_tile256<__half>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+      return launch_fwd_tile256<__nv_bfloat16>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+    }
     if (dtype == SKB_F16) return D <= 64 ? SKB_FWD(__half, 64) : SKB_FWD(__half, 128);
     return D <= 64 ? SKB_FWD(__nv_bfloat16, 64) : SKB_FWD(__nv_bfloat16, 128);
 #undef SKB_FWD

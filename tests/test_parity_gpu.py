@@ -101,7 +101,7 @@ def test_decode_vs_reference(skb, name):
     lens_d = None if lens is None else lens.cuda()
     from stackkernels_b200.launchers import flash_decode as core
     impls = ["general"]
-    if c["dtype"] in ("fp16", "bf16") and c["D"] <= 128 and c["Hq"] // c["Hkv"] <= 64:
+    if c["dtype"] in ("fp16", "bf16") and c["Hq"] // c["Hkv"] <= 64:
         impls.append("sm100")          # the group-per-CTA tensor-core kernel
     for impl in impls:
         for splits in (0, 1, 3):
@@ -127,6 +127,11 @@ PADDED_DECODE_CASES = {
     "fp16_mqa32_d96": dict(B=2, Hq=32, Hkv=1, Scap=2100, D=96, dtype="fp16", seed=74, lens=[2100, 1]),
     "bf16_gqa64_d80": dict(B=2, Hq=128, Hkv=2, Scap=1024, D=80, dtype="bf16", seed=75, lens=[1000, 0]),
     "bf16_gqa24_d128": dict(B=1, Hq=48, Hkv=2, Scap=3000, D=128, dtype="bf16", seed=76, lens=[2999]),
+    # 128 < D <= 256 (64-row tiles of 256 columns on tcgen05, any group up to 128) and a 128-head group
+    "bf16_gqa4_d256": dict(B=3, Hq=8, Hkv=2, Scap=1100, D=256, dtype="bf16", seed=77, lens=[1100, 0, 65]),
+    "fp16_mqa32_d256": dict(B=2, Hq=32, Hkv=1, Scap=2000, D=256, dtype="fp16", seed=78, lens=None),
+    "bf16_gqa8_d192": dict(B=2, Hq=16, Hkv=2, Scap=900, D=192, dtype="bf16", seed=79, lens=[900, 333]),
+    "fp16_mqa128_d128": dict(B=2, Hq=128, Hkv=1, Scap=1500, D=128, dtype="fp16", seed=80, lens=[1500, 129]),
 }
 
 
@@ -169,6 +174,11 @@ TC_BWD_CASES = {
     "bf16_gqa_s256_d96_full": dict(B=2, Hq=4, Hkv=1, Sq=256, Sk=256, D=96, causal=False, dtype="bf16", seed=59),
     "bf16_mha_s130_d32_causal": dict(B=1, Hq=2, Hkv=2, Sq=130, Sk=130, D=32, causal=True, dtype="bf16", seed=60),
     "fp16_gqa_s192_d120_causal": dict(B=1, Hq=4, Hkv=2, Sq=192, Sk=192, D=120, causal=True, dtype="fp16", seed=61),
+    # 128 < D <= 256: one-tile tcgen05 forward (decode_tc.cuh); the backward stays on the general kernels
+    "bf16_gqa_s300_d256_causal": dict(B=1, Hq=4, Hkv=2, Sq=300, Sk=300, D=256, causal=True, dtype="bf16", seed=62),
+    "fp16_mha_s200x333_d256_causal": dict(B=2, Hq=2, Hkv=2, Sq=200, Sk=333, D=256, causal=True, dtype="fp16", seed=63),
+    "bf16_mqa_s333x200_d192_causal": dict(B=1, Hq=4, Hkv=1, Sq=333, Sk=200, D=192, causal=True, dtype="bf16", seed=64),
+    "fp16_gqa_s256x200_d160_full": dict(B=1, Hq=4, Hkv=2, Sq=256, Sk=200, D=160, causal=False, dtype="fp16", seed=65),
 }
 
 
@@ -193,7 +203,7 @@ def test_tensor_core_backward_vs_oracle(skb, name):
         assert_parity(o, eo, c["dtype"], f"{name}[{impl}] O")
         assert_parity(lse, el, c["dtype"], f"{name}[{impl}] LSE")
     edq, edk, edv = orc.attention_backward(do, q, k, v, causal=c["causal"])
-    for impl in ("general", "sm100"):
+    for impl in (("general", "sm100") if D <= 128 else ("general",)):
         dq, dk, dv = flash_attn_bwd(dod, qd, kd, vd, o, lse, is_causal=c["causal"], impl=impl)
         torch.cuda.synchronize()
         assert_parity(dq, edq, c["dtype"], f"{name}[{impl}] dQ")

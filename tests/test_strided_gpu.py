@@ -59,6 +59,19 @@ def test_forward_backward_on_transposed_views(skb, dtype, D, Hq, Hkv, Sq, Sk, ca
     assert skb._lib.device_status() == 0
 
 
+def test_forward_d256_on_transposed_views(skb):
+    from oracle import attention_oracle as orc
+    from stackkernels_b200.launchers import flash_attn_fwd
+    xq, xk, xv = (_bshd(2, 260, h, 256, torch.bfloat16, i).cuda() for i, h in enumerate((4, 2, 2)))
+    q, k, v = (t.transpose(1, 2) for t in (xq, xk, xv))
+    o, lse = flash_attn_fwd(q, k, v, is_causal=True)
+    oc, lsec = flash_attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), is_causal=True)
+    assert torch.equal(o, oc) and torch.equal(lse, lsec)
+    eo, el = orc.attention_forward(q.cpu(), k.cpu(), v.cpu(), causal=True)
+    assert_parity(o, eo, "bf16", "strided D=256 O")
+    assert_parity(lse, el, "bf16", "strided D=256 LSE")
+
+
 def test_autograd_on_packed_qkv(skb):
     """q, k, v sliced out of one packed (B,S,3,H,D) projection and transposed, through the public API."""
     from oracle import attention_oracle as orc
@@ -82,7 +95,7 @@ def test_autograd_on_packed_qkv(skb):
 
 
 @pytest.mark.parametrize("dtype,D,Hq,Hkv", [("bf16", 128, 8, 2), ("fp16", 128, 64, 2), ("bf16", 96, 48, 2),
-                                            ("fp16", 64, 4, 4)])
+                                            ("fp16", 64, 4, 4), ("bf16", 256, 8, 2)])
 def test_decode_on_bshd_cache(skb, dtype, D, Hq, Hkv):
     """KV cache stored (B,S,H_kv,D) and viewed as (B,H_kv,S,D); q a view of a (B,1,H_q,D) projection."""
     from _cases import DT
