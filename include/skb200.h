@@ -124,6 +124,21 @@ int skb_decode_strided(const void* q, const int64_t* q_strides, const void* k_ca
                        int dtype, float scale, int num_splits, int impl,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* Decode over a paged KV cache: the cache is a pool of pages, k_pages / v_pages: (num_pages, Hkv, page_size, D)
+ * addressed through element strides {page, head, row} (so a (num_pages, page_size, Hkv, D) pool works as well),
+ * and block_table: (B, max_pages) int32 names the page of each logical block of each sequence; sequence b
+ * attends to its first cache_seqlens[b] rows (clamped to [0, max_pages * page_size]; entries of block_table past
+ * a sequence's own pages are never read).  page_size: a power of two >= 8.  The reference reserves this op
+ * without implementing it (src/stackkernels/_core/attention/paged.py:1-3); results are those of skb_decode on
+ * the gathered cache.  Group kernels only (16-bit, D <= 256): SKB_ERR_UNSUPPORTED otherwise.  Workspace and
+ * num_splits as for skb_decode with Scap = max_pages * page_size. */
+int skb_decode_paged(const void* q, const int64_t* q_strides, const void* k_pages, const int64_t* k_strides,
+                     const void* v_pages, const int64_t* v_strides, const int32_t* block_table, int max_pages,
+                     const int32_t* cache_seqlens, void* o, const int64_t* o_strides, float* lse,
+                     int B, int Hq, int Hkv, int num_pages, int page_size, int D,
+                     int dtype, float scale, int num_splits,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* Decode for callers that must not allocate device memory.
  *
  * Some hosts of this library run where an allocation is off the table: an inference server whose

@@ -110,6 +110,26 @@ def decode_forward(q, k_cache, v_cache, cache_seqlens=None, scale=None):
     return torch.cat(outs), torch.cat(lses)
 
 
+def decode_paged_forward(q, k_pages, v_pages, block_table, cache_seqlens, scale=None):
+    """Decode over a paged cache: gather each sequence's pages into a dense cache, then ``decode_forward``.
+
+    ``k_pages`` / ``v_pages`` ``(num_pages, Hkv, page_size, D)``; ``block_table`` ``(B, max_pages)``.  The reference
+    only reserves this op (src/stackkernels/_core/attention/paged.py:1-3); its meaning here is "decode on the
+    cache the block table describes", so the oracle is the gather followed by the pinned decode oracle."""
+    bsz, page = q.shape[0], k_pages.shape[2]
+    outs, lses = [], []
+    for b in range(bsz):
+        n = int(cache_seqlens[b])
+        npg = (n + page - 1) // page
+        idx = block_table[b, :npg].long()
+        kb = k_pages[idx].permute(1, 0, 2, 3).reshape(1, k_pages.shape[1], npg * page, k_pages.shape[3])[:, :, :n]
+        vb = v_pages[idx].permute(1, 0, 2, 3).reshape(1, v_pages.shape[1], npg * page, v_pages.shape[3])[:, :, :n]
+        o, l = attention_forward(q[b:b + 1], kb, vb, causal=False, scale=scale)
+        outs.append(o)
+        lses.append(l)
+    return torch.cat(outs), torch.cat(lses)
+
+
 def forward_sliced(q, k, v, causal=False, scale=None, units=None):
     """Evaluate ``attention_forward`` one (batch, kv-head) unit at a time.
 

@@ -40,6 +40,14 @@ inline Strides contiguous_strides(int H, int S, int D) {
   return Strides{(long long)H * S * D, (long long)S * D, (long long)D};
 }
 
+// Paged KV cache: logical row r of sequence b lives in page block_table[b * max_pages + r / page_size] at row
+// r % page_size.  block_table == nullptr means a dense cache (page = batch index, row = r).  sub_rows is the
+// number of rows one bulk copy fetches: min(page_size, rows of a kernel tile).
+struct PagedKv {
+  const int32_t* block_table;
+  int max_pages, page_size, sub_rows;
+};
+
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
 
 // Load 16 bytes (Vec16<T>::N elements) from global memory and widen to fp32.

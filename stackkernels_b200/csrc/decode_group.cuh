@@ -65,8 +65,8 @@ template <typename T, int HD, int MT>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const T* __restrict__ q, const Strides q_str, const int32_t* __restrict__ seqlens,
-              float* __restrict__ part_o,
-              float2* __restrict__ part_ml, int Hq, int Hkv, int Scap, int D, int nsplit, float scale_log2) {
+              const PagedKv pg, float* __restrict__ part_o, float2* __restrict__ part_ml, int Hq, int Hkv, int Scap,
+              int D, int nsplit, float scale_log2) {
   // D <= HD (a multiple of 8) is the head dimension in memory: the tensor maps cover D columns, so the bulk
   // copies zero columns [D, HD) of the K/V tiles; Q is read and the partial O written D columns wide.
   constexpr int TILE = tile_bytes<HD>();
@@ -118,9 +118,25 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (!ok) break;
         ptx::mbar_expect_tx(full(st), 2 * TILE);
         const int row = start + j * kTileN;
-        for (int h = 0; h < HD / 64; ++h) {
-          ptx::tma_load_4d(sK(st) + h * kBoxBytes, &tm_k, h * 64, row, hkv, b, full(st));
-          ptx::tma_load_4d(sV(st) + h * kBoxBytes, &tm_v, h * 64, row, hkv, b, full(st));
+        if (pg.block_table == nullptr) {
+          for (int h = 0; h < HD / 64; ++h) {
+            ptx::tma_load_4d(sK(st) + h * kBoxBytes, &tm_k, h * 64, row, hkv, b, full(st));
+            ptx::tma_load_4d(sV(st) + h * kBoxBytes, &tm_v, h * 64, row, hkv, b, full(st));
+          }
+        } else {
+          // paged: one copy per sub_rows rows, each from the page the block table names.  Sub-tiles that start
+          // past the end of the sequence re-read the last valid one (their scores are masked and their V rows
+          // zeroed below), so the table is never read past the sequence's own pages.
+          const int last_sub = (len - 1) / pg.sub_rows * pg.sub_rows;
+          for (int sub = 0; sub < kTileN; sub += pg.sub_rows) {
+            const int lr = min(row + sub, last_sub);
+            const int page = pg.block_table[(size_t)b * pg.max_pages + lr / pg.page_size];
+            const int prow = lr % pg.page_size;
+            for (int h = 0; h < HD / 64; ++h) {
+              ptx::tma_load_4d(sK(st) + h * kBoxBytes + sub * 128, &tm_k, h * 64, prow, hkv, page, full(st));
+              ptx::tma_load_4d(sV(st) + h * kBoxBytes + sub * 128, &tm_v, h * 64, prow, hkv, page, full(st));
+            }
+          }
         }
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (4u << 16));

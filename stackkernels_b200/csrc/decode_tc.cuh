@@ -52,6 +52,7 @@ enum Bar {
 
 // Arguments that differ between the two uses of the kernel.
 struct DecodeArgs {            // PREFILL = false
+  PagedKv pg;                  // block_table == nullptr: dense cache
   const int32_t* seqlens;      // (B,) or null
   float* part_o;               // (B, Hq, nsplit, D) fp32
   float2* part_ml;             // (B, Hq, nsplit) (max, sum), max in the log2 domain
@@ -98,12 +99,12 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   const int qtile = PREFILL ? (pre.causal ? gridDim.x - 1 - blockIdx.x : blockIdx.x) : 0;
   const int q0 = qtile * 128;
   const int shift = PREFILL ? Sk - pre.Sq : 0;                 // bottom-right causal alignment
-  int start, end;
+  int start, end, len = Sk;
   if (PREFILL) {
     start = 0;
     end = pre.causal ? max(0, min(Sk, q0 + 128 + shift)) : Sk;
   } else {
-    const int len = dec.seqlens ? min(max(dec.seqlens[b], 0), Sk) : Sk;
+    len = dec.seqlens ? min(max(dec.seqlens[b], 0), Sk) : Sk;
     const int chunk = cdiv(cdiv(len, dec.nsplit), KV) * KV;
     start = split * chunk;
     end = min(len, start + chunk);
@@ -137,6 +138,25 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         else           // rows = query heads of this group (q as {D, Hq, B}); rows >= G: other heads or zero fill
           ptx::tma_load_3d(sQ + h * kBoxBytes, &tm_q, h * 64, hkv * G, b, bar(Q_FULL));
       }
+      // One K or V tile.  Dense: one copy per 64-column box.  Paged: one copy per sub_rows rows and box, each
+      // from the page the block table names; sub-tiles that start past the end of the sequence re-read the last
+      // valid one (their scores are masked and their V rows zeroed), so the table is never read past the
+      // sequence's own pages.
+      const bool paged = !PREFILL && dec.pg.block_table != nullptr;
+      const int last_sub = paged ? (len - 1) / dec.pg.sub_rows * dec.pg.sub_rows : 0;
+      auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, int row, uint32_t full_bar) {
+        if (!paged) {
+          for (int h = 0; h < HD / 64; ++h) ptx::tma_load_4d(dst + h * C::kKvBox, tm, h * 64, row, hkv, b, full_bar);
+          return;
+        }
+        for (int sub = 0; sub < KV; sub += dec.pg.sub_rows) {
+          const int lr = min(row + sub, last_sub);
+          const int page = dec.pg.block_table[(size_t)b * dec.pg.max_pages + lr / dec.pg.page_size];
+          const int prow = lr % dec.pg.page_size;
+          for (int h = 0; h < HD / 64; ++h)
+            ptx::tma_load_4d(dst + h * C::kKvBox + sub * 128, tm, h * 64, prow, hkv, page, full_bar);
+        }
+      };
       bool ok = true;
       for (int j = 0; j < nt && ok; ++j) {
         const int st = j % STAGES;
@@ -145,13 +165,11 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         ok = ptx::mbar_wait(bar(K_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(K_FULL + st), C::kKvBytes);
-        for (int h = 0; h < HD / 64; ++h)
-          ptx::tma_load_4d(sK(st) + h * C::kKvBox, &tm_k, h * 64, row, hkv, b, bar(K_FULL + st));
+        load_tile(sK(st), &tm_k, row, bar(K_FULL + st));
         ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(V_FULL + st), C::kKvBytes);
-        for (int h = 0; h < HD / 64; ++h)
-          ptx::tma_load_4d(sV(st) + h * C::kKvBox, &tm_v, h * 64, row, hkv, b, bar(V_FULL + st));
+        load_tile(sV(st), &tm_v, row, bar(V_FULL + st));
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (13u << 16));
     }

@@ -241,7 +241,7 @@ int launch_fwd_tile256(const void* q, const Strides& qs, const void* k, const St
   if (int rc = make_map_4d(&mv, dt, v, D, Sk, Hkv, B, vs, C::kKvRows)) return rc;
   auto kern = dtc::tile_kernel<T, 256, true>;
   if (int rc = set_smem(kern, C::kSmemBytes)) return rc;
-  const dtc::DecodeArgs dec{nullptr, nullptr, nullptr, 1};
+  const dtc::DecodeArgs dec{PagedKv{nullptr, 0, 0, 0}, nullptr, nullptr, nullptr, 1};
   const dtc::PrefillArgs<T> pre{(T*)o, os, lse, Sq, causal};
   kern<<<dim3(cdiv(Sq, 128), Hq, B), dtc::kThreads, C::kSmemBytes, st>>>(mq, mk, mv, dec, pre, Hq, Hkv, Sk, D,
                                                                         scale * kLog2e);
@@ -336,32 +336,54 @@ bool decode_group_covers(int Hq, int Hkv, int D, int dtype) {
 // bulk copies.
 bool decode_uses_tcgen05(int Hq, int Hkv, int D) { return D > 128 || (D > 64 && Hq / Hkv > 16); }
 
+// The KV cache as the group kernels see it.  Dense: (B, Hkv, Scap, D) with strides, block_table null.
+// Paged: (num_pages, Hkv, page_size, D) with strides {page, head, row} plus a (B, max_pages) block table;
+// Scap is then the logical capacity max_pages * page_size.
+struct KvCache {
+  const void *k, *v;
+  Strides ks, vs;
+  const int32_t* block_table;
+  int max_pages, page_size, num_pages;
+  bool paged() const { return block_table != nullptr; }
+};
+
+// Tensor maps over K and V for tiles of `tile_rows` rows, and the paging record the kernels take.
+int make_kv_maps(CUtensorMap* mk, CUtensorMap* mv, PagedKv* pg, int dt, const KvCache& kv, int D, int Scap, int Hkv, int B,
+                 int tile_rows) {
+  const int sub = kv.paged() ? (kv.page_size < tile_rows ? kv.page_size : tile_rows) : tile_rows;
+  const int rows = kv.paged() ? kv.page_size : Scap, outer = kv.paged() ? kv.num_pages : B;
+  if (int rc = make_map_4d(mk, dt, kv.k, D, rows, Hkv, outer, kv.ks, sub)) return rc;
+  if (int rc = make_map_4d(mv, dt, kv.v, D, rows, Hkv, outer, kv.vs, sub)) return rc;
+  *pg = PagedKv{kv.block_table, kv.max_pages, kv.page_size, sub};
+  return SKB_OK;
+}
+
 template <typename T, int HD, int MT>
-int launch_decode_group(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const Strides& qs,
+int launch_decode_group(const CUtensorMap& mk, const CUtensorMap& mv, const PagedKv& pg, const void* q, const Strides& qs,
                         const int32_t* lens, float* part_o, float2* part_ml, int B, int Hq, int Hkv, int Scap, int D,
                         int nsplit, float scale, cudaStream_t st) {
   auto kern = dgrp::decode_kernel<T, HD, MT>;
   constexpr size_t smem = dgrp::smem_bytes<HD>();
   if (int rc = set_smem(kern, smem)) return rc;
-  kern<<<dim3(nsplit, Hkv, B), dgrp::kThreads, smem, st>>>(mk, mv, (const T*)q, qs, lens, part_o, part_ml, Hq, Hkv, Scap,
-                                                          D, nsplit, scale * kLog2e);
+  kern<<<dim3(nsplit, Hkv, B), dgrp::kThreads, smem, st>>>(mk, mv, (const T*)q, qs, lens, pg, part_o, part_ml, Hq, Hkv,
+                                                          Scap, D, nsplit, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
 
 template <typename T, int HD>
-int launch_decode_tile(const void* q, const Strides& qs, const void* kc, const Strides& ks, const void* vc,
-                       const Strides& vs, const int32_t* lens, void* o, const Strides& os, float* lse, int B, int Hq,
-                       int Hkv, int Scap, int D, int nsplit, float scale, float* part_o, float2* part_ml, cudaStream_t st) {
+int launch_decode_tile(const void* q, const Strides& qs, const KvCache& kv, const int32_t* lens, void* o, const Strides& os,
+                       float* lse, int B, int Hq, int Hkv, int Scap, int D, int nsplit, float scale, float* part_o,
+                       float2* part_ml, cudaStream_t st) {
   using C = dtc::Cfg<HD>;
   const int dt = DtypeOf<T>::value;
   CUtensorMap mq, mk, mv;
+  PagedKv pg;
   if (int rc = make_map_q_heads(&mq, dt, q, D, Hq, B, qs)) return rc;
-  if (int rc = make_map_4d(&mk, dt, kc, D, Scap, Hkv, B, ks, C::kKvRows)) return rc;
-  if (int rc = make_map_4d(&mv, dt, vc, D, Scap, Hkv, B, vs, C::kKvRows)) return rc;
+  if (int rc = make_kv_maps(&mk, &mv, &pg, dt, kv, D, Scap, Hkv, B, C::kKvRows)) return rc;
   auto kern = dtc::tile_kernel<T, HD, false>;
   if (int rc = set_smem(kern, C::kSmemBytes)) return rc;
-  const dtc::DecodeArgs dec{lens, part_o, part_ml, nsplit};
+  const dtc::DecodeArgs dec{pg, lens, part_o, part_ml, nsplit};
   const dtc::PrefillArgs<T> pre{nullptr, Strides{0, 0, 0}, nullptr, 1, 0};
   kern<<<dim3(nsplit, Hkv, B), dtc::kThreads, C::kSmemBytes, st>>>(mq, mk, mv, dec, pre, Hq, Hkv, Scap, D, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
@@ -371,21 +393,21 @@ int launch_decode_tile(const void* q, const Strides& qs, const void* kc, const S
 }
 
 template <typename T>
-int decode_group(const void* q, const Strides& qs, const void* kc, const Strides& ks, const void* vc, const Strides& vs,
-                 const int32_t* lens, void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Scap, int D,
-                 int nsplit, float scale, float* part_o, float2* part_ml, cudaStream_t st) {
+int decode_group(const void* q, const Strides& qs, const KvCache& kv, const int32_t* lens, void* o, const Strides& os,
+                 float* lse, int B, int Hq, int Hkv, int Scap, int D, int nsplit, float scale, float* part_o,
+                 float2* part_ml, cudaStream_t st) {
   const int dt = DtypeOf<T>::value;
   const int G = Hq / Hkv;
   int rc;
   if (decode_uses_tcgen05(Hq, Hkv, D)) {
     // wide groups / wide heads: tcgen05 kernel with the group's heads as the MMA M dimension (decode_tc.cuh)
-    return D > 128 ? launch_decode_tile<T, 256>(q, qs, kc, ks, vc, vs, lens, o, os, lse, B, Hq, Hkv, Scap, D, nsplit, scale, part_o, part_ml, st)
-                   : launch_decode_tile<T, 128>(q, qs, kc, ks, vc, vs, lens, o, os, lse, B, Hq, Hkv, Scap, D, nsplit, scale, part_o, part_ml, st);
+    return D > 128 ? launch_decode_tile<T, 256>(q, qs, kv, lens, o, os, lse, B, Hq, Hkv, Scap, D, nsplit, scale, part_o, part_ml, st)
+                   : launch_decode_tile<T, 128>(q, qs, kv, lens, o, os, lse, B, Hq, Hkv, Scap, D, nsplit, scale, part_o, part_ml, st);
   }
   CUtensorMap mk, mv;
-  if (int r2 = make_map_4d(&mk, dt, kc, D, Scap, Hkv, B, ks, dgrp::kTileN)) return r2;
-  if (int r2 = make_map_4d(&mv, dt, vc, D, Scap, Hkv, B, vs, dgrp::kTileN)) return r2;
-#define SKB_DG(HD_, MT_) launch_decode_group<T, HD_, MT_>(mk, mv, q, qs, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st)
+  PagedKv pg;
+  if (int r2 = make_kv_maps(&mk, &mv, &pg, dt, kv, D, Scap, Hkv, B, dgrp::kTileN)) return r2;
+#define SKB_DG(HD_, MT_) launch_decode_group<T, HD_, MT_>(mk, mv, pg, q, qs, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st)
   if (D <= 64) rc = G <= 16 ? SKB_DG(64, 1) : (G <= 32 ? SKB_DG(64, 2) : SKB_DG(64, 4));
   else rc = G <= 16 ? SKB_DG(128, 1) : (G <= 32 ? SKB_DG(128, 2) : SKB_DG(128, 4));
 #undef SKB_DG
@@ -632,24 +654,25 @@ size_t skb_decode_workspace_bytes(int B, int Hq, int Hkv, int Scap, int D, int d
 }
 
 namespace {
-int decode_impl(const void* q, const Strides& qs, const void* k_cache, const Strides& ks, const void* v_cache,
-                const Strides& vs, const int32_t* cache_seqlens, void* o, const Strides& os, float* lse, int B, int Hq,
-                int Hkv, int Scap, int D, int dtype, float scale, int num_splits, int impl, void* workspace,
-                size_t workspace_bytes, cudaStream_t st) {
-  if (!q || !k_cache || !v_cache || !o) return SKB_ERR_NULL;
+int decode_impl(const void* q, const Strides& qs, const KvCache& kv, const int32_t* cache_seqlens, void* o,
+                const Strides& os, float* lse, int B, int Hq, int Hkv, int Scap, int D, int dtype, float scale,
+                int num_splits, int impl, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!q || !kv.k || !kv.v || !o) return SKB_ERR_NULL;
   if (int rc = check_common(B, Hq, Hkv, 1, Scap, D, dtype)) return rc;
-  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o)) return SKB_ERR_ALIGN;
-  const bool dense = same_strides(qs, contiguous_strides(Hq, 1, D), B, Hq, 1) &&
+  if (!aligned16(q) || !aligned16(kv.k) || !aligned16(kv.v) || !aligned16(o)) return SKB_ERR_ALIGN;
+  const int kv_rows = kv.paged() ? kv.page_size : Scap, kv_outer = kv.paged() ? kv.num_pages : B;
+  const bool dense = !kv.paged() && same_strides(qs, contiguous_strides(Hq, 1, D), B, Hq, 1) &&
                      same_strides(os, contiguous_strides(Hq, 1, D), B, Hq, 1) &&
-                     same_strides(ks, contiguous_strides(Hkv, Scap, D), B, Hkv, Scap) &&
-                     same_strides(vs, contiguous_strides(Hkv, Scap, D), B, Hkv, Scap);
+                     same_strides(kv.ks, contiguous_strides(Hkv, Scap, D), B, Hkv, Scap) &&
+                     same_strides(kv.vs, contiguous_strides(Hkv, Scap, D), B, Hkv, Scap);
   const bool group_ok = decode_group_covers(Hq, Hkv, D, dtype);
   if (impl == SKB_IMPL_SM100 && !group_ok) return SKB_ERR_UNSUPPORTED;
   const bool use_group = group_ok && impl != SKB_IMPL_GENERAL;
   if (!dense) {
+    // strided or paged caches: only the bulk-copy kernels can address them
     if (!use_group) return SKB_ERR_UNSUPPORTED;
-    if (!strides_ok(q, qs, B, Hq, 1) || !strides_ok(o, os, B, Hq, 1) || !strides_ok(k_cache, ks, B, Hkv, Scap) ||
-        !strides_ok(v_cache, vs, B, Hkv, Scap))
+    if (!strides_ok(q, qs, B, Hq, 1) || !strides_ok(o, os, B, Hq, 1) || !strides_ok(kv.k, kv.ks, kv_outer, Hkv, kv_rows) ||
+        !strides_ok(kv.v, kv.vs, kv_outer, Hkv, kv_rows))
       return SKB_ERR_ALIGN;
   }
   if (num_splits <= 0) num_splits = skb_decode_num_splits(B, Hq, Hkv, Scap, D, dtype, 0);
@@ -661,14 +684,14 @@ int decode_impl(const void* q, const Strides& qs, const void* k_cache, const Str
   float* part_o = (float*)workspace;
   float2* part_ml = (float2*)((char*)workspace + align_up(n * D * sizeof(float), 256));
   if (use_group) {
-#define SKB_DGRP(T_) decode_group<T_>(q, qs, k_cache, ks, v_cache, vs, cache_seqlens, o, os, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st)
+#define SKB_DGRP(T_) decode_group<T_>(q, qs, kv, cache_seqlens, o, os, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st)
     return dtype == SKB_F16 ? SKB_DGRP(__half) : SKB_DGRP(__nv_bfloat16);
 #undef SKB_DGRP
   }
   switch (dtype) {
-    case SKB_F32: return decode_general<float>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
-    case SKB_F16: return decode_general<__half>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
-    default: return decode_general<__nv_bfloat16>(q, k_cache, v_cache, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+    case SKB_F32: return decode_general<float>(q, kv.k, kv.v, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+    case SKB_F16: return decode_general<__half>(q, kv.k, kv.v, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
+    default: return decode_general<__nv_bfloat16>(q, kv.k, kv.v, cache_seqlens, o, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st);
   }
 }
 }  // namespace
@@ -678,8 +701,9 @@ int skb_decode(const void* q, const void* k_cache, const void* v_cache, const in
                void* workspace, size_t workspace_bytes, void* stream) {
   if (B < 1 || Hq < 1 || Hkv < 1 || Scap < 1 || D < 1) return SKB_ERR_SHAPE;
   const Strides qs = contiguous_strides(Hq, 1, D), ks = contiguous_strides(Hkv, Scap, D);
-  return decode_impl(q, qs, k_cache, ks, v_cache, ks, cache_seqlens, o, qs, lse, B, Hq, Hkv, Scap, D, dtype, scale,
-                     num_splits, impl, workspace, workspace_bytes, (cudaStream_t)stream);
+  const KvCache kv{k_cache, v_cache, ks, ks, nullptr, 0, 0, 0};
+  return decode_impl(q, qs, kv, cache_seqlens, o, qs, lse, B, Hq, Hkv, Scap, D, dtype, scale, num_splits, impl, workspace,
+                     workspace_bytes, (cudaStream_t)stream);
 }
 
 int skb_decode_strided(const void* q, const int64_t* q_strides, const void* k_cache, const int64_t* k_strides,
@@ -687,9 +711,25 @@ int skb_decode_strided(const void* q, const int64_t* q_strides, const void* k_ca
                        const int64_t* o_strides, float* lse, int B, int Hq, int Hkv, int Scap, int D, int dtype,
                        float scale, int num_splits, int impl, void* workspace, size_t workspace_bytes, void* stream) {
   if (!q_strides || !k_strides || !v_strides || !o_strides) return SKB_ERR_NULL;
-  return decode_impl(q, strides_from(q_strides), k_cache, strides_from(k_strides), v_cache, strides_from(v_strides),
-                     cache_seqlens, o, strides_from(o_strides), lse, B, Hq, Hkv, Scap, D, dtype, scale, num_splits, impl,
-                     workspace, workspace_bytes, (cudaStream_t)stream);
+  const KvCache kv{k_cache, v_cache, strides_from(k_strides), strides_from(v_strides), nullptr, 0, 0, 0};
+  return decode_impl(q, strides_from(q_strides), kv, cache_seqlens, o, strides_from(o_strides), lse, B, Hq, Hkv, Scap, D,
+                     dtype, scale, num_splits, impl, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int skb_decode_paged(const void* q, const int64_t* q_strides, const void* k_pages, const int64_t* k_strides,
+                     const void* v_pages, const int64_t* v_strides, const int32_t* block_table, int max_pages,
+                     const int32_t* cache_seqlens, void* o, const int64_t* o_strides, float* lse, int B, int Hq, int Hkv,
+                     int num_pages, int page_size, int D, int dtype, float scale, int num_splits, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  if (!q_strides || !k_strides || !v_strides || !o_strides || !block_table || !cache_seqlens) return SKB_ERR_NULL;
+  // pages of 8, 16, 32, ... rows: a tile is then a whole number of pages or a page a whole number of tiles
+  if (max_pages < 1 || num_pages < 1 || page_size < 8 || (page_size & (page_size - 1)) != 0) return SKB_ERR_SHAPE;
+  if ((long long)max_pages * page_size > 0x7fffffffLL) return SKB_ERR_TOO_LARGE;
+  const KvCache kv{k_pages, v_pages, strides_from(k_strides), strides_from(v_strides), block_table, max_pages, page_size,
+                   num_pages};
+  return decode_impl(q, strides_from(q_strides), kv, cache_seqlens, o, strides_from(o_strides), lse, B, Hq, Hkv,
+                     max_pages * page_size, D, dtype, scale, num_splits, SKB_IMPL_SM100, workspace, workspace_bytes,
+                     (cudaStream_t)stream);
 }
 
 int skb_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, const int32_t* cache_seqlens, void* o,

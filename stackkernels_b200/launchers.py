@@ -209,3 +209,53 @@ def flash_decode(q, k, v, sm_scale=None, cache_seqlens=None, return_lse=False, n
                             ws.data_ptr(), ws_bytes, _stream(q))
     _raise_for_status(rc, "flash_decode")
     return (out, lse) if return_lse else out
+
+
+def flash_decode_paged(q, k_pages, v_pages, block_table, cache_seqlens, sm_scale=None, return_lse=False, num_splits=0):
+    """Split-KV decode over a paged KV cache (the op ``src/stackkernels/_core/attention/paged.py:1-3`` reserves).
+
+    ``q`` ``(B, H_q, 1, D)``; ``k_pages`` / ``v_pages`` ``(num_pages, H_kv, page_size, D)`` -- any strided view
+    with D contiguous, e.g. a ``(num_pages, page_size, H_kv, D)`` pool seen through ``transpose(1, 2)``;
+    ``block_table`` int32 ``(B, max_pages)``: page of each logical block of each sequence; ``cache_seqlens`` int32
+    ``(B,)``.  Equals ``flash_decode`` on the gathered cache.  16-bit tensors, D <= 256, page_size a power of two
+    >= 8."""
+    if q.ndim != 4 or k_pages.ndim != 4 or v_pages.ndim != 4:
+        raise ValueError(f"Expected 4D tensors, got q={q.ndim}D, k_pages={k_pages.ndim}D, v_pages={v_pages.ndim}D")
+    B, H_q, S_q, D = q.shape
+    num_pages, H_kv, page_size, D_k = k_pages.shape
+    if tuple(v_pages.shape) != tuple(k_pages.shape):
+        raise ValueError(f"k_pages and v_pages must have one shape, got {tuple(k_pages.shape)} and {tuple(v_pages.shape)}")
+    if D != D_k:
+        raise ValueError(f"Head dimension mismatch: q={D}, k={D_k}, v={D_k}")
+    if H_q % H_kv != 0:
+        raise ValueError(f"Query heads ({H_q}) must be divisible by KV heads ({H_kv}) for GQA/MQA")
+    assert S_q == 1, f"flash_decode requires q_len == 1, got {S_q}"
+    dt = _check_device_dtype(q, k_pages, v_pages)
+    if block_table.ndim != 2 or block_table.shape[0] != B:
+        raise ValueError(f"block_table must have shape ({B}, max_pages), got {tuple(block_table.shape)}")
+    if cache_seqlens.ndim != 1 or cache_seqlens.shape[0] != B:
+        raise ValueError(f"cache_seqlens must have shape ({B},), got {tuple(cache_seqlens.shape)}")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    block_table = block_table.to(device=q.device, dtype=torch.int32).contiguous()
+    cache_seqlens = cache_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
+    max_pages = block_table.shape[1]
+    if not all(_addressable(t) for t in (q, k_pages, v_pages)):
+        raise NotImplementedError("flash_decode_paged: needs 16-bit tensors with a contiguous head dimension, strides "
+                                  "that are multiples of 8 elements and 16-byte aligned bases")
+    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H_q, 1), dtype=torch.float32, device=q.device)
+    lib = _lib.load()
+    cap = max_pages * page_size
+    if num_splits <= 0:
+        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+        num_splits = lib.skb_decode_num_splits(B, H_q, H_kv, cap, D, dt, sms)
+    ws_bytes = lib.skb_decode_workspace_bytes(B, H_q, H_kv, cap, D, dt, num_splits)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = lib.skb_decode_paged(q.data_ptr(), _strides3(q), k_pages.data_ptr(), _strides3(k_pages), v_pages.data_ptr(),
+                                  _strides3(v_pages), block_table.data_ptr(), max_pages, cache_seqlens.data_ptr(),
+                                  out.data_ptr(), _strides3(out), lse.data_ptr(), B, H_q, H_kv, num_pages, page_size, D,
+                                  dt, float(sm_scale), int(num_splits), ws.data_ptr(), ws_bytes, _stream(q))
+    _raise_for_status(rc, "flash_decode_paged")
+    return (out, lse) if return_lse else out

@@ -83,3 +83,27 @@ def test_sliced_evaluation_is_exact():
         g = q.shape[1] // k.shape[1]
         assert torch.equal(os_[0], o[b, h * g:(h + 1) * g])
         assert torch.allclose(ls_[0], lse[b, h * g:(h + 1) * g], atol=1e-6)
+
+
+def test_paged_decode_oracle_is_decode_on_the_gathered_cache():
+    """The paged oracle must equal the (pinned) decode oracle on the dense cache its block table describes."""
+    g = torch.Generator().manual_seed(3)
+    B, Hq, Hkv, D, page, max_pages = 3, 4, 2, 32, 8, 6
+    lens = torch.tensor([41, 0, 8], dtype=torch.int32)
+    num_pages = 12
+    k = torch.randn(num_pages, Hkv, page, D, generator=g)
+    v = torch.randn(num_pages, Hkv, page, D, generator=g)
+    q = torch.randn(B, Hq, 1, D, generator=g)
+    perm = torch.randperm(num_pages, generator=g)
+    table = torch.full((B, max_pages), -1, dtype=torch.int32)
+    table[0, :6] = perm[:6].to(torch.int32)
+    table[2, :1] = perm[6:7].to(torch.int32)
+    dense_k = torch.zeros(B, Hkv, max_pages * page, D)
+    dense_v = torch.zeros_like(dense_k)
+    for b in range(B):
+        for p in range((int(lens[b]) + page - 1) // page):
+            dense_k[b, :, p * page:(p + 1) * page] = k[int(table[b, p])]
+            dense_v[b, :, p * page:(p + 1) * page] = v[int(table[b, p])]
+    o, lse = orc.decode_paged_forward(q, k, v, table, lens)
+    eo, el = orc.decode_forward(q, dense_k, dense_v, cache_seqlens=lens)
+    assert torch.equal(o, eo) and torch.equal(lse, el)

@@ -1,0 +1,87 @@
+"""Paged-KV decode: equals decode on the gathered cache.  The reference reserves the op without implementing it
+(src/stackkernels/_core/attention/paged.py:1-3), so the expected values come from the decode oracle applied to the
+cache the block table describes, and from this library's own dense decode on that gathered cache (bit for bit: the
+same kernels in the same split order)."""
+import pytest
+import torch
+
+from _parity import assert_parity
+
+pytestmark = pytest.mark.gpu
+
+CASES = {
+    # name: (dtype, B, Hq, Hkv, D, page_size, max_pages, lens, pool layout)
+    "bf16_gqa4_d128_p16": ("bf16", 4, 8, 2, 128, 16, 70, [1100, 1, 0, 513], "nhsd"),
+    "fp16_gqa8_d64_p64": ("fp16", 3, 16, 2, 64, 64, 20, [1280, 700, 65], "nhsd"),
+    "bf16_gqa4_d128_p256": ("bf16", 2, 8, 2, 128, 256, 6, [1536, 300], "nhsd"),
+    "fp16_mqa64_d128_p16": ("fp16", 2, 64, 1, 128, 16, 160, [2500, 17], "nshd"),
+    "bf16_mqa32_d96_p128": ("bf16", 2, 32, 1, 96, 128, 12, [1536, 1000], "nshd"),
+    "bf16_gqa8_d256_p32": ("bf16", 3, 16, 2, 256, 32, 40, [1280, 31, 650], "nshd"),
+    "fp16_gqa4_d80_p8": ("fp16", 2, 8, 2, 80, 8, 100, [799, 8], "nhsd"),
+}
+
+
+def _make(case):
+    from _cases import DT
+    dtype, B, Hq, Hkv, D, page, max_pages, lens, layout = case
+    dt = DT[dtype]
+    g = torch.Generator().manual_seed(hash(case[1:7]) % (2 ** 31))
+    need = sum((n + page - 1) // page for n in lens)
+    num_pages = need + 5
+    perm = torch.randperm(num_pages, generator=g)
+    table = torch.full((B, max_pages), -1, dtype=torch.int32)        # entries past a sequence's pages are poison
+    at = 0
+    for b, n in enumerate(lens):
+        npg = (n + page - 1) // page
+        table[b, :npg] = perm[at:at + npg].to(torch.int32)
+        at += npg
+    if layout == "nhsd":
+        k = torch.randn(num_pages, Hkv, page, D, generator=g).to(dt)
+        v = torch.randn(num_pages, Hkv, page, D, generator=g).to(dt)
+    else:                                                             # pool stored (pages, page_size, Hkv, D)
+        k = torch.randn(num_pages, page, Hkv, D, generator=g).to(dt).transpose(1, 2)
+        v = torch.randn(num_pages, page, Hkv, D, generator=g).to(dt).transpose(1, 2)
+    q = torch.randn(B, Hq, 1, D, generator=g).to(dt)
+    return dtype, q, k, v, table, torch.tensor(lens, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_paged_decode(name):
+    import stackkernels_b200 as skb
+    from oracle import attention_oracle as orc
+    from stackkernels_b200 import _lib
+    dtype, q, k, v, table, lens = _make(CASES[name])
+    eo, el = orc.decode_paged_forward(q, k, v, table, lens)
+    kd, vd = k.cuda(), v.cuda()                      # .cuda() keeps the pool's strides
+    assert kd.stride() == k.stride()
+    for splits in (0, 1, 3):
+        o, lse = skb.flash_decode_paged(q.cuda(), kd, vd, table.cuda(), lens.cuda(), return_lse=True, num_splits=splits)
+        torch.cuda.synchronize()
+        assert_parity(o, eo, dtype, f"{name}[splits={splits}] O")
+        assert_parity(lse, el, dtype, f"{name}[splits={splits}] LSE")
+    # bit-equal to the dense decode on the gathered cache
+    B, page, max_pages = q.shape[0], k.shape[2], table.shape[1]
+    dense_k = torch.zeros(B, k.shape[1], max_pages * page, k.shape[3], dtype=k.dtype)
+    dense_v = torch.zeros_like(dense_k)
+    for b in range(B):
+        for p in range((int(lens[b]) + page - 1) // page):
+            dense_k[b, :, p * page:(p + 1) * page] = k[int(table[b, p])]
+            dense_v[b, :, p * page:(p + 1) * page] = v[int(table[b, p])]
+    from stackkernels_b200.launchers import flash_decode
+    od, lsed = flash_decode(q.cuda(), dense_k.cuda(), dense_v.cuda(), cache_seqlens=lens.cuda(), return_lse=True)
+    o, lse = skb.flash_decode_paged(q.cuda(), kd, vd, table.cuda(), lens.cuda(), return_lse=True)
+    assert torch.equal(o, od) and torch.equal(lse, lsed)
+    assert _lib.device_status() == 0
+
+
+def test_paged_decode_rejects_what_it_cannot_run():
+    import stackkernels_b200 as skb
+    q = torch.randn(1, 4, 1, 64).cuda()
+    k = torch.randn(4, 2, 16, 64).cuda()
+    table = torch.zeros(1, 2, dtype=torch.int32).cuda()
+    lens = torch.tensor([20], dtype=torch.int32).cuda()
+    with pytest.raises(NotImplementedError):                      # fp32: no group kernel
+        skb.flash_decode_paged(q, k, k, table, lens)
+    qh, kh = q.half(), torch.randn(4, 2, 12, 64).half().cuda()
+    with pytest.raises(ValueError):                               # page size not a power of two
+        skb.flash_decode_paged(qh, kh, kh, table, lens)
