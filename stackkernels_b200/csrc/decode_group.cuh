@@ -108,38 +108,55 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   if (warp == kComputeWarps) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      ptx::prefetch_tmap(&tm_k);
-      ptx::prefetch_tmap(&tm_v);
-      bool ok = true;
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int st = j % kStages;
-        ok = ptx::mbar_wait(empty(st), (uint32_t)((j / kStages) & 1) ^ 1u, s_abort);
-        if (!ok) break;
-        ptx::mbar_expect_tx(full(st), 2 * TILE);
-        const int row = start + j * kTileN;
-        if (pg.block_table == nullptr) {
+    if (pg.block_table == nullptr) {
+      if (lane == 0) {
+        // dense cache: one lane, one copy per 64-column box
+        ptx::prefetch_tmap(&tm_k);
+        ptx::prefetch_tmap(&tm_v);
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; ++j) {
+          const int st = j % kStages;
+          ok = ptx::mbar_wait(empty(st), (uint32_t)((j / kStages) & 1) ^ 1u, s_abort);
+          if (!ok) break;
+          ptx::mbar_expect_tx(full(st), 2 * TILE);
+          const int row = start + j * kTileN;
           for (int h = 0; h < HD / 64; ++h) {
             ptx::tma_load_4d(sK(st) + h * kBoxBytes, &tm_k, h * 64, row, hkv, b, full(st));
             ptx::tma_load_4d(sV(st) + h * kBoxBytes, &tm_v, h * 64, row, hkv, b, full(st));
           }
-        } else {
-          // paged: one copy per sub_rows rows, each from the page the block table names.  Sub-tiles that start
-          // past the end of the sequence re-read the last valid one (their scores are masked and their V rows
-          // zeroed below), so the table is never read past the sequence's own pages.
-          const int last_sub = (len - 1) / pg.sub_rows * pg.sub_rows;
-          for (int sub = 0; sub < kTileN; sub += pg.sub_rows) {
-            const int lr = min(row + sub, last_sub);
-            const int page = pg.block_table[(size_t)b * pg.max_pages + lr / pg.page_size];
-            const int prow = lr % pg.page_size;
-            for (int h = 0; h < HD / 64; ++h) {
-              ptx::tma_load_4d(sK(st) + h * kBoxBytes + sub * 128, &tm_k, h * 64, prow, hkv, page, full(st));
-              ptx::tma_load_4d(sV(st) + h * kBoxBytes + sub * 128, &tm_v, h * 64, prow, hkv, page, full(st));
-            }
+        }
+        if (!ok) atomicCAS(&g_dev_status, 0u, (4u << 16));
+      }
+    } else if (ntiles > 0) {
+      // paged cache: the whole warp.  Lane i owns sub-tile i (sub_rows rows): it reads that sub-tile's page from
+      // the block table and issues its copies.  Sub-tiles that start past the end of the sequence re-read the last
+      // valid one (their scores are masked and their V rows zeroed below), so the table is never read past the
+      // sequence's own pages.
+      if (lane == 0) { ptx::prefetch_tmap(&tm_k); ptx::prefetch_tmap(&tm_v); }
+      const int nsub = kTileN / pg.sub_rows;
+      const int last_sub = (len - 1) / pg.sub_rows * pg.sub_rows;
+      bool ok = true;
+      for (int j = 0; j < ntiles; ++j) {
+        const int st = j % kStages;
+        int page = 0, prow = 0;
+        if (lane < nsub) {
+          const int lr = min(start + j * kTileN + lane * pg.sub_rows, last_sub);
+          page = pg.block_table[(size_t)b * pg.max_pages + lr / pg.page_size];
+          prow = lr % pg.page_size;
+        }
+        ok = ptx::mbar_wait_warp(empty(st), (uint32_t)((j / kStages) & 1) ^ 1u, s_abort);
+        if (!ok) break;
+        if (lane == 0) ptx::mbar_expect_tx(full(st), 2 * TILE);
+        __syncwarp();
+        if (lane < nsub) {
+          const uint32_t off = (uint32_t)(lane * pg.sub_rows) * 128u;
+          for (int h = 0; h < HD / 64; ++h) {
+            ptx::tma_load_4d(sK(st) + h * kBoxBytes + off, &tm_k, h * 64, prow, hkv, page, full(st));
+            ptx::tma_load_4d(sV(st) + h * kBoxBytes + off, &tm_v, h * 64, prow, hkv, page, full(st));
           }
         }
       }
-      if (!ok) atomicCAS(&g_dev_status, 0u, (4u << 16));
+      if (!ok && lane == 0) atomicCAS(&g_dev_status, 0u, (4u << 16));
     }
     return;   // the producer warp takes no part in the compute-warp barriers below
   }

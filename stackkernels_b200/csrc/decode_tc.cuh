@@ -128,8 +128,9 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   auto tS = [&](int buf) -> uint32_t { return tmem + 128u * (uint32_t)buf; };
 
   if (warp == 0) {
+    // -------------------------------------------------------------------- TMA producer
+    const bool paged = !PREFILL && dec.pg.block_table != nullptr;
     if (lane == 0 && nt > 0) {
-      // ------------------------------------------------------------------ TMA producer
       ptx::prefetch_tmap(&tm_q); ptx::prefetch_tmap(&tm_k); ptx::prefetch_tmap(&tm_v);
       ptx::mbar_expect_tx(bar(Q_FULL), C::kQBytes);
       for (int h = 0; h < HD / 64; ++h) {
@@ -138,40 +139,61 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         else           // rows = query heads of this group (q as {D, Hq, B}); rows >= G: other heads or zero fill
           ptx::tma_load_3d(sQ + h * kBoxBytes, &tm_q, h * 64, hkv * G, b, bar(Q_FULL));
       }
-      // One K or V tile.  Dense: one copy per 64-column box.  Paged: one copy per sub_rows rows and box, each
-      // from the page the block table names; sub-tiles that start past the end of the sequence re-read the last
-      // valid one (their scores are masked and their V rows zeroed), so the table is never read past the
-      // sequence's own pages.
-      const bool paged = !PREFILL && dec.pg.block_table != nullptr;
-      const int last_sub = paged ? (len - 1) / dec.pg.sub_rows * dec.pg.sub_rows : 0;
-      auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, int row, uint32_t full_bar) {
-        if (!paged) {
-          for (int h = 0; h < HD / 64; ++h) ptx::tma_load_4d(dst + h * C::kKvBox, tm, h * 64, row, hkv, b, full_bar);
-          return;
-        }
-        for (int sub = 0; sub < KV; sub += dec.pg.sub_rows) {
-          const int lr = min(row + sub, last_sub);
-          const int page = dec.pg.block_table[(size_t)b * dec.pg.max_pages + lr / dec.pg.page_size];
-          const int prow = lr % dec.pg.page_size;
+    }
+    if (!paged) {
+      if (lane == 0 && nt > 0) {
+        // dense K/V: one lane, one copy per 64-column box
+        bool ok = true;
+        for (int j = 0; j < nt && ok; ++j) {
+          const int st = j % STAGES;
+          const uint32_t ph = (uint32_t)((j / STAGES) & 1) ^ 1u;
+          const int row = start + j * KV;
+          ok = ptx::mbar_wait(bar(K_EMPTY + st), ph, s_abort);
+          if (!ok) break;
+          ptx::mbar_expect_tx(bar(K_FULL + st), C::kKvBytes);
           for (int h = 0; h < HD / 64; ++h)
-            ptx::tma_load_4d(dst + h * C::kKvBox + sub * 128, tm, h * 64, prow, hkv, page, full_bar);
+            ptx::tma_load_4d(sK(st) + h * C::kKvBox, &tm_k, h * 64, row, hkv, b, bar(K_FULL + st));
+          ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
+          if (!ok) break;
+          ptx::mbar_expect_tx(bar(V_FULL + st), C::kKvBytes);
+          for (int h = 0; h < HD / 64; ++h)
+            ptx::tma_load_4d(sV(st) + h * C::kKvBox, &tm_v, h * 64, row, hkv, b, bar(V_FULL + st));
         }
-      };
+        if (!ok) atomicCAS(&g_dev_status, 0u, (13u << 16));
+      }
+    } else if (nt > 0) {
+      // paged K/V: the whole warp.  Lane i owns sub-tile i (sub_rows rows): it reads that sub-tile's page from the
+      // block table and issues its copies, so the lookups and the copy issue run in parallel across lanes.
+      // Sub-tiles that start past the end of the sequence re-read the last valid one (their scores are masked and
+      // their V rows zeroed), so the table is never read past the sequence's own pages.
+      const int sub_rows = dec.pg.sub_rows, nsub = KV / sub_rows;
+      const int last_sub = (len - 1) / sub_rows * sub_rows;
       bool ok = true;
-      for (int j = 0; j < nt && ok; ++j) {
+      for (int j = 0; j < nt; ++j) {
         const int st = j % STAGES;
         const uint32_t ph = (uint32_t)((j / STAGES) & 1) ^ 1u;
-        const int row = start + j * KV;
-        ok = ptx::mbar_wait(bar(K_EMPTY + st), ph, s_abort);
+        int page = 0, prow = 0;
+        if (lane < nsub) {
+          const int lr = min(start + j * KV + lane * sub_rows, last_sub);
+          page = dec.pg.block_table[(size_t)b * dec.pg.max_pages + lr / dec.pg.page_size];
+          prow = lr % dec.pg.page_size;
+        }
+        ok = ptx::mbar_wait_warp(bar(K_EMPTY + st), ph, s_abort);
         if (!ok) break;
-        ptx::mbar_expect_tx(bar(K_FULL + st), C::kKvBytes);
-        load_tile(sK(st), &tm_k, row, bar(K_FULL + st));
-        ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
+        if (lane == 0) ptx::mbar_expect_tx(bar(K_FULL + st), C::kKvBytes);
+        __syncwarp();
+        if (lane < nsub)
+          for (int h = 0; h < HD / 64; ++h)
+            ptx::tma_load_4d(sK(st) + h * C::kKvBox + lane * sub_rows * 128, &tm_k, h * 64, prow, hkv, page, bar(K_FULL + st));
+        ok = ptx::mbar_wait_warp(bar(V_EMPTY + st), ph, s_abort);
         if (!ok) break;
-        ptx::mbar_expect_tx(bar(V_FULL + st), C::kKvBytes);
-        load_tile(sV(st), &tm_v, row, bar(V_FULL + st));
+        if (lane == 0) ptx::mbar_expect_tx(bar(V_FULL + st), C::kKvBytes);
+        __syncwarp();
+        if (lane < nsub)
+          for (int h = 0; h < HD / 64; ++h)
+            ptx::tma_load_4d(sV(st) + h * C::kKvBox + lane * sub_rows * 128, &tm_v, h * 64, prow, hkv, page, bar(V_FULL + st));
       }
-      if (!ok) atomicCAS(&g_dev_status, 0u, (13u << 16));
+      if (!ok && lane == 0) atomicCAS(&g_dev_status, 0u, (13u << 16));
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------------- MMA issuer (whole warp, one lane issues)
