@@ -124,6 +124,31 @@ int skb_decode_strided(const void* q, const int64_t* q_strides, const void* k_ca
                        int dtype, float scale, int num_splits, int impl,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* Variable-length (packed) prefill: B sequences packed back to back, q, o, dO, dQ: (total_q, Hq, D) and
+ * k, v, dK, dV: (total_k, Hkv, D), each with two int64 element strides {token, head} (D contiguous, strides
+ * positive multiples of 8, bases 16-byte aligned); cu_seqlens_q / cu_seqlens_k: (B+1,) int32 device prefix sums
+ * (sequence b owns rows [cu[b], cu[b+1])); max_seqlen_q / max_seqlen_k: host upper bounds of the sequence
+ * lengths (they size the grid).  Every sequence is attended on its own with the same semantics as skb_attn_fwd
+ * (bottom-right causal mask per sequence, empty or fully masked rows give O = 0, LSE = -inf).  lse: (Hq, total_q)
+ * fp32.  The reference reserves this op without implementing it (src/stackkernels/_core/attention/varlen.py:1-3);
+ * results are those of skb_attn_fwd / skb_attn_bwd applied per sequence.  Tensor-core paths only: 16-bit,
+ * D <= 256 forward, D <= 128 backward (SKB_ERR_UNSUPPORTED otherwise). */
+int skb_attn_fwd_varlen(const void* q, const int64_t* q_strides, const void* k, const int64_t* k_strides,
+                        const void* v, const int64_t* v_strides, void* o, const int64_t* o_strides, float* lse,
+                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                        int B, int Hq, int Hkv, int total_q, int total_k, int max_seqlen_q, int max_seqlen_k, int D,
+                        int dtype, int causal, float scale, void* stream);
+size_t skb_attn_bwd_varlen_workspace_bytes(int B, int Hq, int total_q, int D);
+int skb_attn_bwd_varlen(const void* dout, const int64_t* dout_strides, const void* q, const int64_t* q_strides,
+                        const void* k, const int64_t* k_strides, const void* v, const int64_t* v_strides,
+                        const void* o, const int64_t* o_strides, const float* lse,
+                        void* dq, const int64_t* dq_strides, void* dk, const int64_t* dk_strides,
+                        void* dv, const int64_t* dv_strides,
+                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                        int B, int Hq, int Hkv, int total_q, int total_k, int max_seqlen_q, int max_seqlen_k, int D,
+                        int dtype, int causal, float scale,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
 /* Decode over a paged KV cache: the cache is a pool of pages, k_pages / v_pages: (num_pages, Hkv, page_size, D)
  * addressed through element strides {page, head, row} (so a (num_pages, page_size, Hkv, D) pool works as well),
  * and block_table: (B, max_pages) int32 names the page of each logical block of each sequence; sequence b

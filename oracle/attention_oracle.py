@@ -130,6 +130,39 @@ def decode_paged_forward(q, k_pages, v_pages, block_table, cache_seqlens, scale=
     return torch.cat(outs), torch.cat(lses)
 
 
+def varlen_forward(q, k, v, cu_q, cu_k, causal=False, scale=None):
+    """Packed variable-length attention: ``attention_forward`` on every sequence by itself.
+
+    ``q`` ``(total_q, Hq, D)``, ``k`` / ``v`` ``(total_k, Hkv, D)``, ``cu_*`` ``(B+1,)`` prefix sums.  Returns
+    (O ``(total_q, Hq, D)`` in q.dtype, LSE ``(Hq, total_q)`` fp32).  The reference only reserves this op
+    (src/stackkernels/_core/attention/varlen.py:1-3); its meaning here is "each sequence as a batch of one"."""
+    outs, lses = [], []
+    for b in range(len(cu_q) - 1):
+        qb = q[int(cu_q[b]):int(cu_q[b + 1])].transpose(0, 1).unsqueeze(0)
+        kb = k[int(cu_k[b]):int(cu_k[b + 1])].transpose(0, 1).unsqueeze(0)
+        vb = v[int(cu_k[b]):int(cu_k[b + 1])].transpose(0, 1).unsqueeze(0)
+        if qb.shape[2] == 0:
+            continue
+        o, l = attention_forward(qb, kb, vb, causal=causal, scale=scale)
+        outs.append(o[0].transpose(0, 1))
+        lses.append(l[0])
+    return torch.cat(outs, 0), torch.cat(lses, 1)
+
+
+def varlen_backward(do, q, k, v, cu_q, cu_k, causal=False, scale=None):
+    """Gradients of ``varlen_forward``: ``attention_backward`` on every sequence by itself."""
+    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+    for b in range(len(cu_q) - 1):
+        q0, q1, k0, k1 = int(cu_q[b]), int(cu_q[b + 1]), int(cu_k[b]), int(cu_k[b + 1])
+        if q1 == q0 or k1 == k0:
+            continue
+        sl = lambda t, a, e: t[a:e].transpose(0, 1).unsqueeze(0)
+        gq, gk, gv = attention_backward(sl(do, q0, q1), sl(q, q0, q1), sl(k, k0, k1), sl(v, k0, k1), causal=causal,
+                                        scale=scale)
+        dq[q0:q1], dk[k0:k1], dv[k0:k1] = gq[0].transpose(0, 1), gk[0].transpose(0, 1), gv[0].transpose(0, 1)
+    return dq, dk, dv
+
+
 def forward_sliced(q, k, v, causal=False, scale=None, units=None):
     """Evaluate ``attention_forward`` one (batch, kv-head) unit at a time.
 

@@ -5,8 +5,10 @@ from .attention import FlashAttention, FlashAttentionFunction, flash_attention, 
 from .embedding import RoPE, RoPEFunction, apply_rope, kv_cache_append, precompute_freqs
 from .host import flash_attention_host
 from .launchers import flash_decode_paged
+from .varlen import FlashAttentionVarlenFunction, flash_attention_varlen
 
-__all__ = ["flash_attention", "flash_decode", "flash_decode_paged", "flash_attention_host", "apply_rope", "RoPE", "RoPEFunction",
+__all__ = ["flash_attention", "flash_attention_varlen", "FlashAttentionVarlenFunction", "flash_decode",
+           "flash_decode_paged", "flash_attention_host", "apply_rope", "RoPE", "RoPEFunction",
            "precompute_freqs", "kv_cache_append", "FlashAttention", "FlashAttentionFunction",
            "get_backend", "set_backend", "options"]
 __version__ = "0.1.0"

@@ -35,6 +35,9 @@ SIGNATURES = {
     "skb_decode_noalloc": (_i, [_vp] * 6 + [_i] * 5 + [_i, _f, _i, _vp]),
     "skb_attn_fwd_strided": (_i, [_vp, _sp] * 4 + [_vp] + [_i] * 6 + [_i, _i, _f, _i, _vp]),
     "skb_attn_bwd_strided": (_i, [_vp, _sp] * 5 + [_vp] + [_vp, _sp] * 3 + [_i] * 6 + [_i, _i, _f, _i, _vp, _sz, _vp]),
+    "skb_attn_fwd_varlen": (_i, [_vp, _sp] * 4 + [_vp, _vp, _vp] + [_i] * 8 + [_i, _i, _f, _vp]),
+    "skb_attn_bwd_varlen_workspace_bytes": (_sz, [_i] * 4),
+    "skb_attn_bwd_varlen": (_i, [_vp, _sp] * 5 + [_vp] + [_vp, _sp] * 3 + [_vp, _vp] + [_i] * 8 + [_i, _i, _f, _vp, _sz, _vp]),
     "skb_decode_paged": (_i, [_vp, _sp] * 3 + [_vp, _i, _vp] + [_vp, _sp] + [_vp] + [_i] * 6 + [_i, _f, _i, _vp, _sz, _vp]),
     "skb_decode_strided": (_i, [_vp, _sp] * 3 + [_vp] + [_vp, _sp] + [_vp] + [_i] * 5 + [_i, _f, _i, _i, _vp, _sz, _vp]),
     "skb_rope": (_i, [_vp] * 4 + [_i] * 10 + [_vp]),

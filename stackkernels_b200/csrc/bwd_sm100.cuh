@@ -118,6 +118,43 @@ bwd_prep_kernel(const T* __restrict__ dout, const Strides do_str, const T* __res
   }
 }
 
+// The same pre-pass for a packed batch: one warp per (padded row, head, sequence).  dO and O are (total_q, Hq, D)
+// tensors addressed as batch 0 of their strides; LSE is (Hq, total_q); delta and lse2 live in the padded row space
+// described at struct Varlen, (Hq, total_pad).
+template <typename T>
+__global__ void __launch_bounds__(256)
+bwd_prep_varlen_kernel(const T* __restrict__ dout, const Strides do_str, const T* __restrict__ o, const Strides o_str,
+                       const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
+                       const Varlen vl, int D) {
+  constexpr int VE = Vec16<T>::N;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5), h = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31;
+  const int qoff = vl.cu_q[b], Sq = vl.cu_q[b + 1] - qoff;
+  if (r >= ((Sq + 127) & ~127)) return;
+  const size_t prow = (size_t)h * vl.total_pad + varlen_pad_off(qoff, b) + r;
+  if (r >= Sq) {
+    if (lane == 0) { delta[prow] = 0.f; lse2[prow] = -INFINITY; }
+    return;
+  }
+  const T* do_row = dout + do_str.at(0, h, qoff + r);
+  const T* o_row = o + o_str.at(0, h, qoff + r);
+  float s = 0.f;
+  for (int c = lane * VE; c < D; c += 32 * VE) {
+    float a[VE], b2[VE];
+    load_vec16<T>(do_row + c, a);
+    load_vec16<T>(o_row + c, b2);
+#pragma unroll
+    for (int i = 0; i < VE; ++i) s += a[i] * b2[i];
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) {
+    delta[prow] = -s;
+    const float l = lse[(size_t)h * vl.total_q + qoff + r];
+    lse2[prow] = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
+  }
+}
+
 // Postprocess: dQ = T(scale * dQ_accumulator); the accumulator is (B*Hq, Sq, D) contiguous, dQ may be strided.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -140,8 +177,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
            const float* __restrict__ lse2, const float* __restrict__ delta, float* __restrict__ dq_acc,
-           T* __restrict__ dk, const Strides dk_str, T* __restrict__ dv, const Strides dv_str, int Hq, int Hkv,
-           int Sq, int Sk, int Sq_pad, int D, int causal,
+           T* __restrict__ dk, const Strides dk_str, T* __restrict__ dv, const Strides dv_str, const Varlen vl, int Hq,
+           int Hkv, int Sq, int Sk, int Sq_pad, int D, int causal,
            float scale, float scale_log2) {
   // The tiles are 128 columns wide; D <= 128 (a multiple of 8) is the head dimension in memory.  The tensor
   // maps cover D columns, so the bulk copies zero columns [D, 128) of Q, K, V and dO, which leaves every
@@ -172,12 +209,30 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int lane = threadIdx.x & 31;
   const int jt = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int G = Hq / Hkv;
+  // Packed batch: rows [qoff, qoff+Sq) of q/dO/dQ and [koff, koff+Sk) of k/v/dK/dV, all in "batch" 0 of the tensor
+  // maps and strides (Sq, Sk as passed in are only the grid's upper bounds); the per-row statistics and the dQ
+  // accumulator are laid out per head: (Hq, total_pad) and (Hq, total_q, D).
+  int qoff = 0, koff = 0, zb = b;
+  if (vl.cu_q != nullptr) {
+    qoff = vl.cu_q[b];
+    Sq = vl.cu_q[b + 1] - qoff;
+    koff = vl.cu_k[b];
+    Sk = vl.cu_k[b + 1] - koff;
+    zb = 0;
+  }
+  const int pad_off = vl.cu_q != nullptr ? varlen_pad_off(qoff, b) : 0;
+  auto stat_base = [&](int head) -> size_t {
+    return vl.cu_q != nullptr ? (size_t)head * vl.total_pad + pad_off : ((size_t)b * Hq + head) * Sq_pad;
+  };
+  auto acc_base = [&](int head) -> size_t {
+    return vl.cu_q != nullptr ? (size_t)head * vl.total_q + qoff : ((size_t)b * Hq + head) * Sq;
+  };
   const int shift = Sk - Sq;
   const int kv0 = jt * kBwdTile;
   const int nq = cdiv(Sq, kBwdQ);                                 // 64-row query chunks per head
   int s_start = 0;
   if (causal) s_start = max(0, kv0 - shift) / kBwdQ;              // first chunk that sees key kv0
-  const int per_head = max(0, nq - s_start);
+  const int per_head = kv0 < Sk ? max(0, nq - s_start) : 0;       // a tile past the end of K/V has nothing to do
   const int n_run = per_head * G;                                  // work units of this CTA
 
   if (threadIdx.x == 0) {
@@ -212,24 +267,25 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ptx::prefetch_tmap(&tm_q); ptx::prefetch_tmap(&tm_k); ptx::prefetch_tmap(&tm_v); ptx::prefetch_tmap(&tm_do);
       ptx::mbar_expect_tx(bar(B_KV_FULL), 2 * kBwdTileBytes);
       for (int h = 0; h < 2; ++h) {
-        ptx::tma_load_4d(sK + h * kBwdBox, &tm_k, h * 64, kv0, hkv, b, bar(B_KV_FULL));
-        ptx::tma_load_4d(sV + h * kBwdBox, &tm_v, h * 64, kv0, hkv, b, bar(B_KV_FULL));
+        ptx::tma_load_4d(sK + h * kBwdBox, &tm_k, h * 64, koff + kv0, hkv, zb, bar(B_KV_FULL));
+        ptx::tma_load_4d(sV + h * kBwdBox, &tm_v, h * 64, koff + kv0, hkv, zb, bar(B_KV_FULL));
       }
       bool ok = true;
       for (int u = 0; u < n_run && ok; ++u) {
         const int st = u % kBwdStages;
         const uint32_t ph = (uint32_t)((u / kBwdStages) & 1) ^ 1u;
-        const int bh = b * Hq + head_of(u), q0 = row_of(u);
+        const int q0 = row_of(u);
+        const size_t stat = stat_base(head_of(u)) + q0;
         ok = ptx::mbar_wait(bar(B_Q_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(B_Q_FULL + st), kBwdQTile + 512);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sQ(st) + h * kBwdQBox, &tm_q, h * 64, q0, head_of(u), b, bar(B_Q_FULL + st));
-        bulk_load_1d(sStat0 + st * 512, lse2 + (size_t)bh * Sq_pad + q0, 256, bar(B_Q_FULL + st));
-        bulk_load_1d(sStat0 + st * 512 + 256, delta + (size_t)bh * Sq_pad + q0, 256, bar(B_Q_FULL + st));
+        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sQ(st) + h * kBwdQBox, &tm_q, h * 64, qoff + q0, head_of(u), zb, bar(B_Q_FULL + st));
+        bulk_load_1d(sStat0 + st * 512, lse2 + stat, 256, bar(B_Q_FULL + st));
+        bulk_load_1d(sStat0 + st * 512 + 256, delta + stat, 256, bar(B_Q_FULL + st));
         ok = ptx::mbar_wait(bar(B_DO_EMPTY + st), ph, s_abort);
         if (!ok) break;
         ptx::mbar_expect_tx(bar(B_DO_FULL + st), kBwdQTile);
-        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sdO(st) + h * kBwdQBox, &tm_do, h * 64, q0, head_of(u), b, bar(B_DO_FULL + st));
+        for (int h = 0; h < 2; ++h) ptx::tma_load_4d(sdO(st) + h * kBwdQBox, &tm_do, h * 64, qoff + q0, head_of(u), zb, bar(B_DO_FULL + st));
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (7u << 16));
     } else if (warp == 1 && n_run > 0) {
@@ -341,8 +397,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (!ok) break;
       if (wq == 0 && lane == 0) SKB_TR(1 + w, u >> 1, 0);
       ptx::tc_fence_after();
-      // visible iff kvidx <= q + shift  <=>  column c >= kvidx - shift - q0
-      const int cmin = causal ? kvidx - shift - q0 : -1;
+      // visible iff kvidx <= q + shift  <=>  column c >= kvidx - shift - q0.  A KV row past the end of the sequence
+      // sees nothing: in a dense batch its K row is zero-filled and harmless, in a packed batch it is the next
+      // sequence's data and must not reach dQ.
+      const int cmin = kvidx >= Sk ? kBwdQ : (causal ? kvidx - shift - q0 : -1);
       uint64_t p2[32];                             // the unit's 64 probabilities of this KV row, as fp32 pairs
       {
         uint32_t pk[32];
@@ -433,7 +491,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         ptx::tmem_wait_ld();
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar(B_RP_FREE + w));
-        float* dst = dq_acc + ((size_t)(b * Hq + head_of(u)) * Sq + q0) * D + r;
+        float* dst = dq_acc + (acc_base(head_of(u)) + q0) * D + r;
         const int q_lim = r < D ? Sq - q0 : 0;       // lanes past the head dimension hold zeros: nothing to add
 #pragma unroll
         for (int c = 0; c < 32; ++c)
@@ -452,10 +510,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     }
     if (ok) {
       ptx::tc_fence_after();
-      const int krow = min(kvidx, Sk - 1);
+      const int krow = koff + max(0, min(kvidx, Sk - 1));
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        T* dst = (which == 0 ? dk + dk_str.at(b, hkv, krow) : dv + dv_str.at(b, hkv, krow)) + 64 * w;
+        T* dst = (which == 0 ? dk + dk_str.at(zb, hkv, krow) : dv + dv_str.at(zb, hkv, krow)) + 64 * w;
         const float mul = which == 0 ? scale : 1.f;
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2) {

@@ -48,6 +48,20 @@ struct PagedKv {
   int max_pages, page_size, sub_rows;
 };
 
+// Packed variable-length batch: sequence b owns rows [cu_q[b], cu_q[b+1]) of the (total_q, H, D) query-side
+// tensors and rows [cu_k[b], cu_k[b+1]) of K and V.  cu_q == nullptr means a dense (B, H, S, D) batch.
+// Per-row fp32 statistics of the backward pass are kept per head in a padded row space of total_pad rows in
+// which sequence b starts at varlen_pad_off(cu_q[b], b): a multiple of 128, computable without a prefix sum,
+// and far enough from its neighbours (floor(a+b) >= floor(a) + floor(b), plus 128 rows per sequence) that every
+// sequence has room for its length rounded up to 128.
+struct Varlen {
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int total_q, total_pad;
+};
+__host__ __device__ inline int varlen_pad_off(int cu, int b) { return (cu & ~127) + 128 * b; }
+inline int varlen_total_pad(int total_q, int B) { return ((total_q + 127) & ~127) + 128 * (B + 1); }
+
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
 
 // Load 16 bytes (Vec16<T>::N elements) from global memory and widen to fp32.

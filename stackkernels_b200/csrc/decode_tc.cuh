@@ -61,8 +61,9 @@ struct DecodeArgs {            // PREFILL = false
 template <typename T> struct PrefillArgs {   // PREFILL = true
   T* o;
   Strides o_str;
-  float* lse;                  // (B, Hq, Sq)
-  int Sq, causal;
+  float* lse;                  // (B, Hq, Sq); packed batch: (Hq, total_q)
+  int Sq, causal;              // packed batch: Sq is only the grid's upper bound
+  Varlen vl;                   // cu_q == nullptr: dense batch
 };
 
 // Sk: rows of the K/V tensors (decode: cache capacity).  D <= HD (a multiple of 8) is the head dimension in
@@ -98,11 +99,20 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   const int hkv = PREFILL ? hq / G : blockIdx.y;
   const int qtile = PREFILL ? (pre.causal ? gridDim.x - 1 - blockIdx.x : blockIdx.x) : 0;
   const int q0 = qtile * 128;
-  const int shift = PREFILL ? Sk - pre.Sq : 0;                 // bottom-right causal alignment
+  // packed batch (prefill only): rows [qoff, qoff+Sq) of q/o and [koff, koff+Sk) of k/v, "batch" 0 of the maps
+  int Sq = PREFILL ? pre.Sq : 1, qoff = 0, koff = 0, zb = b;
+  if (PREFILL && pre.vl.cu_q != nullptr) {
+    qoff = pre.vl.cu_q[b];
+    Sq = pre.vl.cu_q[b + 1] - qoff;
+    koff = pre.vl.cu_k[b];
+    Sk = pre.vl.cu_k[b + 1] - koff;
+    zb = 0;
+  }
+  const int shift = PREFILL ? Sk - Sq : 0;                     // bottom-right causal alignment
   int start, end, len = Sk;
   if (PREFILL) {
     start = 0;
-    end = pre.causal ? max(0, min(Sk, q0 + 128 + shift)) : Sk;
+    end = q0 < Sq ? (pre.causal ? max(0, min(Sk, q0 + 128 + shift)) : Sk) : 0;
   } else {
     len = dec.seqlens ? min(max(dec.seqlens[b], 0), Sk) : Sk;
     const int chunk = cdiv(cdiv(len, dec.nsplit), KV) * KV;
@@ -135,7 +145,7 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       ptx::mbar_expect_tx(bar(Q_FULL), C::kQBytes);
       for (int h = 0; h < HD / 64; ++h) {
         if (PREFILL)   // rows = query positions of head hq (q as {D, Sq, Hq, B})
-          ptx::tma_load_4d(sQ + h * kBoxBytes, &tm_q, h * 64, q0, hq, b, bar(Q_FULL));
+          ptx::tma_load_4d(sQ + h * kBoxBytes, &tm_q, h * 64, qoff + q0, hq, zb, bar(Q_FULL));
         else           // rows = query heads of this group (q as {D, Hq, B}); rows >= G: other heads or zero fill
           ptx::tma_load_3d(sQ + h * kBoxBytes, &tm_q, h * 64, hkv * G, b, bar(Q_FULL));
       }
@@ -152,12 +162,12 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           if (!ok) break;
           ptx::mbar_expect_tx(bar(K_FULL + st), C::kKvBytes);
           for (int h = 0; h < HD / 64; ++h)
-            ptx::tma_load_4d(sK(st) + h * C::kKvBox, &tm_k, h * 64, row, hkv, b, bar(K_FULL + st));
+            ptx::tma_load_4d(sK(st) + h * C::kKvBox, &tm_k, h * 64, koff + row, hkv, zb, bar(K_FULL + st));
           ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
           if (!ok) break;
           ptx::mbar_expect_tx(bar(V_FULL + st), C::kKvBytes);
           for (int h = 0; h < HD / 64; ++h)
-            ptx::tma_load_4d(sV(st) + h * C::kKvBox, &tm_v, h * 64, row, hkv, b, bar(V_FULL + st));
+            ptx::tma_load_4d(sV(st) + h * C::kKvBox, &tm_v, h * 64, koff + row, hkv, zb, bar(V_FULL + st));
         }
         if (!ok) atomicCAS(&g_dev_status, 0u, (13u << 16));
       }
@@ -359,7 +369,8 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       if (PREFILL) {
         const int grow = q0 + r;
         const float inv = seen ? 1.f / l : 0.f;
-        T* orow = pre.o + pre.o_str.at(b, hq, min(grow, pre.Sq - 1));
+        T* orow = pre.o + pre.o_str.at(zb, hq, qoff + max(0, min(grow, Sq - 1)));
+        const size_t lse_base = pre.vl.cu_q != nullptr ? (size_t)hq * pre.vl.total_q + qoff : ((size_t)b * Hq + hq) * Sq;
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t orr[32];
@@ -370,7 +381,7 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
             for (int i = 0; i < 32; ++i) orr[i] = 0u;
           }
-          if (grow < pre.Sq) {
+          if (grow < Sq) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               if (c * 32 + i >= D) break;
@@ -383,7 +394,7 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             }
           }
         }
-        if (grow < pre.Sq) pre.lse[((size_t)b * Hq + hq) * pre.Sq + grow] = seen ? (m + log2f(l)) * kLn2 : -INFINITY;
+        if (grow < Sq) pre.lse[lse_base + grow] = seen ? (m + log2f(l)) * kLn2 : -INFINITY;
       } else {
         // partial results for the combine kernel
         const size_t pbase = ((size_t)b * Hq + (size_t)hkv * G + min(r, G - 1)) * dec.nsplit + split;

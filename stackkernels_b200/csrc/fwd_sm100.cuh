@@ -77,7 +77,8 @@ template <typename T, int HD>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, T* __restrict__ o, const Strides o_str,
-           float* __restrict__ lse, int Hq, int Hkv, int Sq, int Sk, int D, int causal, float scale_log2) {
+           float* __restrict__ lse, const Varlen vl, int Hq, int Hkv, int Sq, int Sk, int D, int causal,
+           float scale_log2) {
   // D <= HD is the head dimension in memory (a multiple of 8): the tensor maps are built over D columns, so
   // the bulk copies fill columns [D, HD) of every Q/K/V tile with zeros and the products are unchanged; only
   // the first D columns of O are stored.
@@ -104,8 +105,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;   // heaviest (latest) causal blocks first
   const int hq = blockIdx.y, b = blockIdx.z;
-  const int bhq = b * Hq + hq;
   const int hkv = hq / (Hq / Hkv);
+  // Packed batch: this CTA's sequence is rows [qoff, qoff+Sq) of q/o and [koff, koff+Sk) of k/v, all in "batch" 0
+  // of the tensor maps (Sq, Sk as passed in are only the grid's upper bounds).  Rows a tile reads past the end of
+  // its sequence are the next sequence's: keys are masked by the end-of-K test, queries are not stored.
+  int qoff = 0, koff = 0, zb = b;
+  if (vl.cu_q != nullptr) {
+    qoff = vl.cu_q[b];
+    Sq = vl.cu_q[b + 1] - qoff;
+    koff = vl.cu_k[b];
+    Sk = vl.cu_k[b + 1] - koff;
+    zb = 0;
+  }
+  const size_t lse_base = vl.cu_q != nullptr ? (size_t)hq * vl.total_q + qoff : ((size_t)b * Hq + hq) * Sq;
   const int row0 = qblk * 2 * kTileM;
   const int shift = Sk - Sq;
 
@@ -143,13 +155,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       auto load_q = [&](int t) {
         ptx::mbar_expect_tx(bar(Q_FULL + t), TILE);
         for (int h = 0; h < HD / 64; ++h)
-          ptx::tma_load_4d(sQ + t * TILE + h * kBoxBytes, &tm_q, h * 64, row0 + t * kTileM, hq, b, bar(Q_FULL + t));
+          ptx::tma_load_4d(sQ + t * TILE + h * kBoxBytes, &tm_q, h * 64, qoff + row0 + t * kTileM, hq, zb, bar(Q_FULL + t));
       };
       auto load_kv = [&](const CUtensorMap* tm, uint32_t sdst, int full0, int j) {
         const int st = j % kStages;
         ptx::mbar_expect_tx(bar(full0 + st), TILE);
         for (int h = 0; h < HD / 64; ++h)
-          ptx::tma_load_4d(sdst + st * TILE + h * kBoxBytes, tm, h * 64, j * kTileN, hkv, b, bar(full0 + st));
+          ptx::tma_load_4d(sdst + st * TILE + h * kBoxBytes, tm, h * 64, koff + j * kTileN, hkv, zb, bar(full0 + st));
       };
       bool ok = true;
       if (ntile[0] > 0) load_q(0);
@@ -340,7 +352,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ptx::tc_fence_after();
       const bool seen = (m != -INFINITY) && l > 0.f;    // false: no visible key in the whole row
       const float inv = seen ? 1.f / l : 0.f;
-      T* orow = o + o_str.at(b, hq, min(grow, Sq - 1));
+      T* orow = o + o_str.at(zb, hq, qoff + max(0, min(grow, Sq - 1)));
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t orr[32];
@@ -364,7 +376,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
       }
-      if (grow < Sq) lse[(size_t)bhq * Sq + grow] = seen ? (m + log2f(l)) * kLn2 : -INFINITY;
+      if (grow < Sq) lse[lse_base + grow] = seen ? (m + log2f(l)) * kLn2 : -INFINITY;
     } else if (lane == 0) {
       atomicCAS(&g_dev_status, 0u, (3u << 16) | (unsigned)warp);
     }

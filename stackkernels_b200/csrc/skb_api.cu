@@ -212,17 +212,19 @@ bool fwd_sm100_covers(int D, int dtype, float scale) {
 template <typename T, int HD>
 int launch_fwd_sm100(const void* q, const Strides& qs, const void* k, const Strides& ks, const void* v, const Strides& vs,
                      void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Sq, int Sk, int D, int causal,
-                     float scale, cudaStream_t st) {
+                     float scale, cudaStream_t st, const Varlen& vl = Varlen{nullptr, nullptr, 0, 0}, int total_k = 0) {
+  // packed batch: the maps cover all total_q / total_k rows as one "batch"; Sq, Sk only size the grid
+  const bool packed = vl.cu_q != nullptr;
   CUtensorMap mq, mk, mv;
   const int dt = DtypeOf<T>::value;
-  if (int rc = make_map_4d(&mq, dt, q, D, Sq, Hq, B, qs)) return rc;
-  if (int rc = make_map_4d(&mk, dt, k, D, Sk, Hkv, B, ks)) return rc;
-  if (int rc = make_map_4d(&mv, dt, v, D, Sk, Hkv, B, vs)) return rc;
+  if (int rc = make_map_4d(&mq, dt, q, D, packed ? vl.total_q : Sq, Hq, packed ? 1 : B, qs)) return rc;
+  if (int rc = make_map_4d(&mk, dt, k, D, packed ? total_k : Sk, Hkv, packed ? 1 : B, ks)) return rc;
+  if (int rc = make_map_4d(&mv, dt, v, D, packed ? total_k : Sk, Hkv, packed ? 1 : B, vs)) return rc;
   auto kern = sm100::fwd_kernel<T, HD>;
   constexpr size_t smem = sm100::fwd_smem_bytes<HD>();
   if (int rc = set_smem(kern, smem)) return rc;
   dim3 grid(cdiv(Sq, 2 * sm100::kTileM), Hq, B);
-  kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, os, lse, Hq, Hkv, Sq, Sk, D, causal, scale * kLog2e);
+  kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, os, lse, vl, Hq, Hkv, Sq, Sk, D, causal, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -232,17 +234,19 @@ int launch_fwd_sm100(const void* q, const Strides& qs, const void* k, const Stri
 template <typename T>
 int launch_fwd_tile256(const void* q, const Strides& qs, const void* k, const Strides& ks, const void* v,
                        const Strides& vs, void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Sq, int Sk,
-                       int D, int causal, float scale, cudaStream_t st) {
+                       int D, int causal, float scale, cudaStream_t st, const Varlen& vl = Varlen{nullptr, nullptr, 0, 0},
+                       int total_k = 0) {
   using C = dtc::Cfg<256>;
+  const bool packed = vl.cu_q != nullptr;
   CUtensorMap mq, mk, mv;
   const int dt = DtypeOf<T>::value;
-  if (int rc = make_map_4d(&mq, dt, q, D, Sq, Hq, B, qs)) return rc;
-  if (int rc = make_map_4d(&mk, dt, k, D, Sk, Hkv, B, ks, C::kKvRows)) return rc;
-  if (int rc = make_map_4d(&mv, dt, v, D, Sk, Hkv, B, vs, C::kKvRows)) return rc;
+  if (int rc = make_map_4d(&mq, dt, q, D, packed ? vl.total_q : Sq, Hq, packed ? 1 : B, qs)) return rc;
+  if (int rc = make_map_4d(&mk, dt, k, D, packed ? total_k : Sk, Hkv, packed ? 1 : B, ks, C::kKvRows)) return rc;
+  if (int rc = make_map_4d(&mv, dt, v, D, packed ? total_k : Sk, Hkv, packed ? 1 : B, vs, C::kKvRows)) return rc;
   auto kern = dtc::tile_kernel<T, 256, true>;
   if (int rc = set_smem(kern, C::kSmemBytes)) return rc;
   const dtc::DecodeArgs dec{PagedKv{nullptr, 0, 0, 0}, nullptr, nullptr, nullptr, 1};
-  const dtc::PrefillArgs<T> pre{(T*)o, os, lse, Sq, causal};
+  const dtc::PrefillArgs<T> pre{(T*)o, os, lse, Sq, causal, vl};
   kern<<<dim3(cdiv(Sq, 128), Hq, B), dtc::kThreads, C::kSmemBytes, st>>>(mq, mk, mv, dec, pre, Hq, Hkv, Sk, D,
                                                                         scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
@@ -292,6 +296,50 @@ struct BwdTensors {
   Strides dos, qs, ks, vs, os, dqs, dks, dvs;
 };
 
+// Packed batch: per-head statistics over the padded row space, fp32 dQ accumulator (Hq, total_q, D).
+BwdWs bwd_varlen_ws(int B, int Hq, int total_q, int D) {
+  const size_t stats = align_up((size_t)Hq * varlen_total_pad(total_q, B) * sizeof(float), 256);
+  BwdWs w;
+  w.delta_off = 0;
+  w.lse2_off = stats;
+  w.dq_off = 2 * stats;
+  w.total = 2 * stats + align_up((size_t)Hq * total_q * D * sizeof(float), 256);
+  return w;
+}
+
+template <typename T>
+int launch_bwd_varlen(const BwdTensors& t, const float* lse, const int32_t* cu_q, const int32_t* cu_k, int B, int Hq,
+                      int Hkv, int total_q, int total_k, int max_sq, int max_sk, int D, int causal, float scale,
+                      void* workspace, cudaStream_t st) {
+  const BwdWs w = bwd_varlen_ws(B, Hq, total_q, D);
+  float* delta = (float*)((char*)workspace + w.delta_off);
+  float* lse2 = (float*)((char*)workspace + w.lse2_off);
+  float* dq_acc = (float*)((char*)workspace + w.dq_off);
+  const Varlen vl{cu_q, cu_k, total_q, varlen_total_pad(total_q, B)};
+  CUtensorMap mq, mk, mv, mdo;
+  const int dt = DtypeOf<T>::value;
+  if (int rc = make_map_4d(&mq, dt, t.q, D, total_q, Hq, 1, t.qs, sm100::kBwdQ)) return rc;
+  if (int rc = make_map_4d(&mdo, dt, t.dout, D, total_q, Hq, 1, t.dos, sm100::kBwdQ)) return rc;
+  if (int rc = make_map_4d(&mk, dt, t.k, D, total_k, Hkv, 1, t.ks)) return rc;
+  if (int rc = make_map_4d(&mv, dt, t.v, D, total_k, Hkv, 1, t.vs)) return rc;
+  const int max_pad = cdiv(max_sq, 128) * 128;
+  sm100::bwd_prep_varlen_kernel<T><<<dim3(max_pad / 8, Hq, B), 256, 0, st>>>((const T*)t.dout, t.dos, (const T*)t.o, t.os,
+                                                                            lse, delta, lse2, vl, D);
+  SKB_CUDA(cudaGetLastError());
+  SKB_CUDA(cudaMemsetAsync(dq_acc, 0, (size_t)Hq * total_q * D * sizeof(float), st));
+  auto kern = sm100::bwd_kernel<T>;
+  if (int rc = set_smem(kern, sm100::kBwdSmemBytes)) return rc;
+  kern<<<dim3(cdiv(max_sk, 128), Hkv, B), sm100::kBwdThreads, sm100::kBwdSmemBytes, st>>>(
+      mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)t.dk, t.dks, (T*)t.dv, t.dvs, vl, Hq, Hkv, max_sq, max_sk, 0, D, causal,
+      scale, scale * kLog2e);
+  SKB_CUDA(cudaGetLastError());
+  // the accumulator is (Hq, total_q, D): the post kernel's (batch*head, row) with one batch of Hq heads
+  const size_t n4 = (size_t)Hq * total_q * D / 4;
+  sm100::bwd_post_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_acc, (T*)t.dq, t.dqs, scale, Hq, total_q, D, n4);
+  SKB_CUDA(cudaGetLastError());
+  return SKB_OK;
+}
+
 template <typename T>
 int launch_bwd_sm100(const BwdTensors& t, const float* lse, int B, int Hq, int Hkv, int Sq, int Sk, int D, int causal,
                      float scale, void* workspace, cudaStream_t st) {
@@ -316,8 +364,8 @@ int launch_bwd_sm100(const BwdTensors& t, const float* lse, int B, int Hq, int H
   auto kern = sm100::bwd_kernel<T>;
   if (int rc = set_smem(kern, sm100::kBwdSmemBytes)) return rc;
   kern<<<dim3(cdiv(Sk, 128), Hkv, B), sm100::kBwdThreads, sm100::kBwdSmemBytes, st>>>(
-      mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)t.dk, t.dks, (T*)t.dv, t.dvs, Hq, Hkv, Sq, Sk, sq_pad, D, causal, scale,
-      scale * kLog2e);
+      mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)t.dk, t.dks, (T*)t.dv, t.dvs, Varlen{nullptr, nullptr, 0, 0}, Hq, Hkv, Sq,
+      Sk, sq_pad, D, causal, scale, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   const size_t n4 = bh * Sq * D / 4;
   sm100::bwd_post_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_acc, (T*)t.dq, t.dqs, scale, Hq, Sq, D, n4);
@@ -384,7 +432,7 @@ int launch_decode_tile(const void* q, const Strides& qs, const KvCache& kv, cons
   auto kern = dtc::tile_kernel<T, HD, false>;
   if (int rc = set_smem(kern, C::kSmemBytes)) return rc;
   const dtc::DecodeArgs dec{pg, lens, part_o, part_ml, nsplit};
-  const dtc::PrefillArgs<T> pre{nullptr, Strides{0, 0, 0}, nullptr, 1, 0};
+  const dtc::PrefillArgs<T> pre{nullptr, Strides{0, 0, 0}, nullptr, 1, 0, Varlen{nullptr, nullptr, 0, 0}};
   kern<<<dim3(nsplit, Hkv, B), dtc::kThreads, C::kSmemBytes, st>>>(mq, mk, mv, dec, pre, Hq, Hkv, Scap, D, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, os, lse, Hq, D, nsplit);
@@ -617,6 +665,75 @@ int skb_attn_bwd_strided(const void* dout, const int64_t* dout_strides, const vo
                      strides_from(o_strides), strides_from(dq_strides), strides_from(dk_strides), strides_from(dv_strides)};
   return attn_bwd_impl(t, lse, B, Hq, Hkv, Sq, Sk, D, dtype, causal, scale, impl, workspace, workspace_bytes,
                        (cudaStream_t)stream);
+}
+
+// ------------------------------------------------------------------------------------ packed (varlen) batches
+namespace {
+Strides packed_strides(const int64_t* p) { return Strides{0, (long long)p[1], (long long)p[0]}; }   // {token, head}
+int check_varlen(int B, int Hq, int Hkv, int total_q, int total_k, int max_sq, int max_sk, int D, int dtype) {
+  if (B < 1 || total_q < 1 || total_k < 1 || max_sq < 1 || max_sk < 1 || max_sq > total_q || max_sk > total_k)
+    return SKB_ERR_SHAPE;
+  return check_common(1, Hq, Hkv, total_q, total_k, D, dtype);
+}
+}  // namespace
+
+int skb_attn_fwd_varlen(const void* q, const int64_t* q_strides, const void* k, const int64_t* k_strides, const void* v,
+                        const int64_t* v_strides, void* o, const int64_t* o_strides, float* lse,
+                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int B, int Hq, int Hkv, int total_q,
+                        int total_k, int max_seqlen_q, int max_seqlen_k, int D, int dtype, int causal, float scale,
+                        void* stream) {
+  if (!q || !k || !v || !o || !lse || !cu_seqlens_q || !cu_seqlens_k || !q_strides || !k_strides || !v_strides || !o_strides)
+    return SKB_ERR_NULL;
+  if (int rc = check_varlen(B, Hq, Hkv, total_q, total_k, max_seqlen_q, max_seqlen_k, D, dtype)) return rc;
+  if (!fwd_sm100_covers(D, dtype, scale)) return SKB_ERR_UNSUPPORTED;
+  const Strides qs = packed_strides(q_strides), ks = packed_strides(k_strides), vs = packed_strides(v_strides),
+                os = packed_strides(o_strides);
+  if (!strides_ok(q, qs, 1, Hq, total_q) || !strides_ok(k, ks, 1, Hkv, total_k) || !strides_ok(v, vs, 1, Hkv, total_k) ||
+      !strides_ok(o, os, 1, Hq, total_q))
+    return SKB_ERR_ALIGN;
+  const Varlen vl{cu_seqlens_q, cu_seqlens_k, total_q, 0};
+  cudaStream_t st = (cudaStream_t)stream;
+#define SKB_FWDV(F_) F_(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, max_seqlen_q, max_seqlen_k, D, causal, scale, st, vl, total_k)
+  if (D > 128) return dtype == SKB_F16 ? SKB_FWDV(launch_fwd_tile256<__half>) : SKB_FWDV(launch_fwd_tile256<__nv_bfloat16>);
+  if (dtype == SKB_F16) return D <= 64 ? SKB_FWDV((launch_fwd_sm100<__half, 64>)) : SKB_FWDV((launch_fwd_sm100<__half, 128>));
+  return D <= 64 ? SKB_FWDV((launch_fwd_sm100<__nv_bfloat16, 64>)) : SKB_FWDV((launch_fwd_sm100<__nv_bfloat16, 128>));
+#undef SKB_FWDV
+}
+
+size_t skb_attn_bwd_varlen_workspace_bytes(int B, int Hq, int total_q, int D) {
+  if (B < 1 || Hq < 1 || total_q < 1 || D < 1) return 0;
+  return bwd_varlen_ws(B, Hq, total_q, D).total;
+}
+
+int skb_attn_bwd_varlen(const void* dout, const int64_t* dout_strides, const void* q, const int64_t* q_strides,
+                        const void* k, const int64_t* k_strides, const void* v, const int64_t* v_strides, const void* o,
+                        const int64_t* o_strides, const float* lse, void* dq, const int64_t* dq_strides, void* dk,
+                        const int64_t* dk_strides, void* dv, const int64_t* dv_strides, const int32_t* cu_seqlens_q,
+                        const int32_t* cu_seqlens_k, int B, int Hq, int Hkv, int total_q, int total_k, int max_seqlen_q,
+                        int max_seqlen_k, int D, int dtype, int causal, float scale, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  if (!dout || !q || !k || !v || !o || !lse || !dq || !dk || !dv || !cu_seqlens_q || !cu_seqlens_k || !dout_strides ||
+      !q_strides || !k_strides || !v_strides || !o_strides || !dq_strides || !dk_strides || !dv_strides)
+    return SKB_ERR_NULL;
+  if (int rc = check_varlen(B, Hq, Hkv, total_q, total_k, max_seqlen_q, max_seqlen_k, D, dtype)) return rc;
+  if (!bwd_sm100_covers(D, dtype)) return SKB_ERR_UNSUPPORTED;
+  const BwdTensors t{dout, q, k, v, o, dq, dk, dv,
+                     packed_strides(dout_strides), packed_strides(q_strides), packed_strides(k_strides),
+                     packed_strides(v_strides), packed_strides(o_strides), packed_strides(dq_strides),
+                     packed_strides(dk_strides), packed_strides(dv_strides)};
+  if (!strides_ok(t.dout, t.dos, 1, Hq, total_q) || !strides_ok(t.q, t.qs, 1, Hq, total_q) ||
+      !strides_ok(t.o, t.os, 1, Hq, total_q) || !strides_ok(t.dq, t.dqs, 1, Hq, total_q) ||
+      !strides_ok(t.k, t.ks, 1, Hkv, total_k) || !strides_ok(t.v, t.vs, 1, Hkv, total_k) ||
+      !strides_ok(t.dk, t.dks, 1, Hkv, total_k) || !strides_ok(t.dv, t.dvs, 1, Hkv, total_k))
+    return SKB_ERR_ALIGN;
+  if (!workspace || !aligned16(workspace) || workspace_bytes < skb_attn_bwd_varlen_workspace_bytes(B, Hq, total_q, D))
+    return SKB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == SKB_F16)
+    return launch_bwd_varlen<__half>(t, lse, cu_seqlens_q, cu_seqlens_k, B, Hq, Hkv, total_q, total_k, max_seqlen_q,
+                                     max_seqlen_k, D, causal, scale, workspace, st);
+  return launch_bwd_varlen<__nv_bfloat16>(t, lse, cu_seqlens_q, cu_seqlens_k, B, Hq, Hkv, total_q, total_k, max_seqlen_q,
+                                          max_seqlen_k, D, causal, scale, workspace, st);
 }
 
 int skb_decode_num_splits(int B, int Hq, int Hkv, int Scap, int D, int dtype, int sm_count) {

@@ -1,0 +1,178 @@
+"""Variable-length (packed) flash attention.
+
+The reference reserves this op without implementing it (``src/stackkernels/_core/attention/varlen.py:1-3``).
+Meaning here: B sequences packed back to back -- ``q`` ``(total_q, H_q, D)``, ``k`` / ``v`` ``(total_k, H_kv, D)``,
+``cu_seqlens_*`` int32 ``(B+1,)`` prefix sums -- and every sequence is attended on its own exactly as
+``flash_attention`` would attend it as a batch of one (same bottom-right causal mask, same LSE).  The tensor-core
+kernels run the packed batch in one launch; shapes they do not cover (fp32, backward at D > 128) are run sequence
+by sequence through ``flash_attention``.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from .launchers import _addressable, _check_device_dtype, _raise_for_status, _stream
+
+
+def _strides2(t):
+    return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), 0)       # {token, head}; third slot unused
+
+
+def _packed_ok(t) -> bool:
+    """``_addressable`` for a ``(total, H, D)`` tensor."""
+    return _addressable(t.unsqueeze(0))
+
+
+def _validate(q, k, v, cu_q, cu_k):
+    if q.ndim != 3 or k.ndim != 3 or v.ndim != 3:
+        raise ValueError(f"Expected packed 3D tensors (total, H, D), got q={q.ndim}D, k={k.ndim}D, v={v.ndim}D")
+    total_q, H_q, D = q.shape
+    total_k, H_kv, D_k = k.shape
+    if tuple(v.shape) != tuple(k.shape):
+        raise ValueError(f"K and V must have one shape, got {tuple(k.shape)} and {tuple(v.shape)}")
+    if D != D_k:
+        raise ValueError(f"Head dimension mismatch: q={D}, k={D_k}, v={D_k}")
+    if H_q % H_kv != 0:
+        raise ValueError(f"Query heads ({H_q}) must be divisible by KV heads ({H_kv}) for GQA/MQA")
+    if cu_q.ndim != 1 or cu_k.ndim != 1 or cu_q.shape[0] != cu_k.shape[0] or cu_q.shape[0] < 2:
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must be 1-D with B+1 entries each")
+    return total_q, total_k, H_q, H_kv, D, cu_q.shape[0] - 1
+
+
+def _cu(t, device):
+    return t.to(device=device, dtype=torch.int32).contiguous()
+
+
+def flash_attn_varlen_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, is_causal=False,
+                          sm_scale=None):
+    """One launch over the packed batch.  Returns ``(out (total_q, H_q, D), lse (H_q, total_q) fp32)``; raises
+    NotImplementedError where the tensor-core kernels do not apply."""
+    total_q, total_k, H_q, H_kv, D, B = _validate(q, k, v, cu_seqlens_q, cu_seqlens_k)
+    dt = _check_device_dtype(q, k, v)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    if not all(_packed_ok(t) for t in (q, k, v)):
+        raise NotImplementedError("packed tensors must be 16-bit with D contiguous, strides multiples of 8 elements "
+                                  "and 16-byte aligned bases")
+    cu_q, cu_k = _cu(cu_seqlens_q, q.device), _cu(cu_seqlens_k, q.device)
+    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.empty((H_q, total_q), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = _lib.load().skb_attn_fwd_varlen(
+            q.data_ptr(), _strides2(q), k.data_ptr(), _strides2(k), v.data_ptr(), _strides2(v), out.data_ptr(),
+            _strides2(out), lse.data_ptr(), cu_q.data_ptr(), cu_k.data_ptr(), B, H_q, H_kv, total_q, total_k,
+            int(min(max_seqlen_q, total_q)), int(min(max_seqlen_k, total_k)), D, dt, int(bool(is_causal)),
+            float(sm_scale), _stream(q))
+    _raise_for_status(rc, "flash_attn_varlen_fwd")
+    return out, lse
+
+
+def flash_attn_varlen_bwd(do, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                          is_causal=False, sm_scale=None):
+    """Returns ``(dq, dk, dv)`` of the packed batch in one launch sequence."""
+    total_q, total_k, H_q, H_kv, D, B = _validate(q, k, v, cu_seqlens_q, cu_seqlens_k)
+    dt = _check_device_dtype(q, k, v, do, out)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    do = do if _packed_ok(do) else do.contiguous()
+    if not all(_packed_ok(t) for t in (do, q, k, v, out)):
+        raise NotImplementedError("packed tensors must be 16-bit with D contiguous, strides multiples of 8 elements "
+                                  "and 16-byte aligned bases")
+    lse = lse.contiguous()
+    if lse.dtype != torch.float32 or tuple(lse.shape) != (H_q, total_q):
+        raise ValueError(f"lse must be float32 of shape {(H_q, total_q)}, got {lse.dtype} {tuple(lse.shape)}")
+    cu_q, cu_k = _cu(cu_seqlens_q, q.device), _cu(cu_seqlens_k, q.device)
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    lib = _lib.load()
+    ws_bytes = lib.skb_attn_bwd_varlen_workspace_bytes(B, H_q, total_q, D)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = lib.skb_attn_bwd_varlen(
+            do.data_ptr(), _strides2(do), q.data_ptr(), _strides2(q), k.data_ptr(), _strides2(k), v.data_ptr(),
+            _strides2(v), out.data_ptr(), _strides2(out), lse.data_ptr(), dq.data_ptr(), _strides2(dq), dk.data_ptr(),
+            _strides2(dk), dv.data_ptr(), _strides2(dv), cu_q.data_ptr(), cu_k.data_ptr(), B, H_q, H_kv, total_q,
+            total_k, int(min(max_seqlen_q, total_q)), int(min(max_seqlen_k, total_k)), D, dt, int(bool(is_causal)),
+            float(sm_scale), ws.data_ptr(), ws_bytes, _stream(q))
+    _raise_for_status(rc, "flash_attn_varlen_bwd")
+    return dq, dk, dv
+
+
+class FlashAttentionVarlenFunction(torch.autograd.Function):
+    """Autograd wrapper over the packed launchers; saves ``(q, k, v, out, lse)`` like ``FlashAttentionFunction``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, max_sq, max_sk, is_causal, sm_scale):
+        out, lse = flash_attn_varlen_fwd(q, k, v, cu_q, cu_k, max_sq, max_sk, is_causal, sm_scale)
+        ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
+        ctx.args = (int(max_sq), int(max_sk), bool(is_causal), sm_scale)
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        max_sq, max_sk, is_causal, sm_scale = ctx.args
+        dq, dk, dv = flash_attn_varlen_bwd(do, q, k, v, out, lse, cu_q, cu_k, max_sq, max_sk, is_causal, sm_scale)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def _covered(q, k, v, need_grad: bool) -> bool:
+    if q.dtype not in (torch.float16, torch.bfloat16) or not all(_packed_ok(t) for t in (q, k, v)):
+        return False
+    D = q.shape[-1]
+    return D % 8 == 0 and (D <= 128 if need_grad else D <= 256)
+
+
+def _per_sequence(q, k, v, cu_q, cu_k, is_causal, sm_scale, want_lse):
+    """Sequence-by-sequence route through ``flash_attention`` for shapes the packed kernels do not cover (reads the
+    prefix sums on the host).  The LSE costs a second forward per sequence and is only computed on request."""
+    from .attention import flash_attention
+    from .launchers import flash_attn_fwd
+    cq, ck = cu_q.tolist(), cu_k.tolist()
+    outs, lses = [], []
+    for b in range(len(cq) - 1):
+        qb = q[cq[b]:cq[b + 1]].transpose(0, 1).unsqueeze(0)
+        kb = k[ck[b]:ck[b + 1]].transpose(0, 1).unsqueeze(0)
+        vb = v[ck[b]:ck[b + 1]].transpose(0, 1).unsqueeze(0)
+        if qb.shape[2] == 0:
+            continue
+        if kb.shape[2] == 0:                       # no keys: O = 0, LSE = -inf, no gradient
+            outs.append(torch.zeros_like(q[cq[b]:cq[b + 1]]))
+            if want_lse:
+                lses.append(torch.full((q.shape[1], qb.shape[2]), float("-inf"), device=q.device))
+            continue
+        o = flash_attention(qb, kb, vb, is_causal=is_causal, sm_scale=sm_scale)
+        outs.append(o[0].transpose(0, 1))
+        if want_lse:
+            with torch.no_grad():
+                lses.append(flash_attn_fwd(qb, kb, vb, is_causal=is_causal, sm_scale=sm_scale)[1][0])
+    return torch.cat(outs, 0), (torch.cat(lses, 1) if want_lse else None)
+
+
+def flash_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, is_causal: bool = False,
+                           sm_scale: float | None = None, *, causal: bool | None = None,
+                           softmax_scale: float | None = None, return_lse: bool = False):
+    """Packed variable-length attention (differentiable).  ``q`` ``(total_q, H_q, D)``, ``k`` / ``v``
+    ``(total_k, H_kv, D)``, ``cu_seqlens_*`` int32 ``(B+1,)``; returns ``out`` ``(total_q, H_q, D)`` and, with
+    ``return_lse``, the natural-log LSE ``(H_q, total_q)``."""
+    if causal is not None:
+        is_causal = causal
+    if softmax_scale is not None:
+        sm_scale = softmax_scale
+    if not q.is_cuda:
+        raise RuntimeError("stackkernels_b200 runs on CUDA tensors only: there is no CPU fallback on this path")
+    _validate(q, k, v, cu_seqlens_q, cu_seqlens_k)
+    need_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v))
+    if _covered(q, k, v, need_grad):
+        cu_q, cu_k = _cu(cu_seqlens_q, q.device), _cu(cu_seqlens_k, q.device)
+        out, lse = FlashAttentionVarlenFunction.apply(q, k, v, cu_q, cu_k, max_seqlen_q, max_seqlen_k, is_causal,
+                                                      sm_scale)
+    else:
+        out, lse = _per_sequence(q, k, v, cu_seqlens_q, cu_seqlens_k, is_causal, sm_scale, return_lse)
+    return (out, lse) if return_lse else out

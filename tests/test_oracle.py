@@ -107,3 +107,20 @@ def test_paged_decode_oracle_is_decode_on_the_gathered_cache():
     o, lse = orc.decode_paged_forward(q, k, v, table, lens)
     eo, el = orc.decode_forward(q, dense_k, dense_v, cache_seqlens=lens)
     assert torch.equal(o, eo) and torch.equal(lse, el)
+
+
+def test_varlen_oracle_is_the_pinned_oracle_per_sequence():
+    """Packed oracle = forward/backward oracle on each sequence alone; for equal lengths it is the batched one."""
+    g = torch.Generator().manual_seed(4)
+    B, S, Hq, Hkv, D = 3, 24, 4, 2, 16
+    q, do = torch.randn(B, Hq, S, D, generator=g), torch.randn(B, Hq, S, D, generator=g)
+    k, v = torch.randn(B, Hkv, S, D, generator=g), torch.randn(B, Hkv, S, D, generator=g)
+    pack = lambda t: t.transpose(1, 2).reshape(B * S, t.shape[1], D)
+    cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32)
+    o, lse = orc.varlen_forward(pack(q), pack(k), pack(v), cu, cu, causal=True)
+    eo, el = orc.attention_forward(q, k, v, causal=True)
+    assert torch.equal(o, pack(eo)) and torch.equal(lse, el.transpose(0, 1).reshape(Hq, B * S))
+    dq, dk, dv = orc.varlen_backward(pack(do), pack(q), pack(k), pack(v), cu, cu, causal=True)
+    edq, edk, edv = orc.attention_backward(do, q, k, v, causal=True)
+    for a, e in ((dq, edq), (dk, edk), (dv, edv)):
+        assert torch.allclose(a, pack(e), atol=1e-6, rtol=0)

@@ -1,0 +1,88 @@
+"""Packed variable-length attention: every sequence attended by itself.  The reference reserves the op without
+implementing it (src/stackkernels/_core/attention/varlen.py:1-3), so the expected values are the pinned forward /
+backward oracle applied per sequence, and the forward must equal this library's dense kernel run on each sequence
+alone bit for bit (same tiles in the same order)."""
+import pytest
+import torch
+
+from _parity import assert_parity
+
+pytestmark = pytest.mark.gpu
+
+CASES = {
+    # name: (dtype, Hq, Hkv, D, lens_q, lens_k, causal, with backward)
+    "bf16_gqa_d128_causal": ("bf16", 4, 2, 128, [300, 129, 1, 640], [300, 129, 1, 640], True, True),
+    "fp16_mha_d64_full": ("fp16", 2, 2, 64, [200, 0, 77], [333, 0, 500], False, True),
+    "bf16_mqa_d96_causal_sq_ne_sk": ("bf16", 4, 1, 96, [130, 257, 64], [200, 257, 300], True, True),
+    "fp16_gqa_d128_causal_long_short": ("fp16", 8, 2, 128, [1000, 5, 5, 5, 260], [1000, 5, 5, 5, 260], True, True),
+    "bf16_gqa_d256_causal": ("bf16", 4, 2, 256, [300, 70, 200], [300, 170, 200], True, False),
+    "fp16_mha_d160_full": ("fp16", 2, 2, 160, [129, 255], [64, 255], False, False),
+}
+
+
+def _make(case):
+    from _cases import DT
+    dtype, Hq, Hkv, D, lq, lk, causal, bwd = case
+    dt = DT[dtype]
+    g = torch.Generator().manual_seed(sum(lq) * 7 + sum(lk) + D)
+    cu_q = torch.tensor([0] + list(torch.tensor(lq).cumsum(0)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(torch.tensor(lk).cumsum(0)), dtype=torch.int32)
+    q = (torch.randn(sum(lq), Hq, D, generator=g) * 0.7).to(dt)
+    k = (torch.randn(sum(lk), Hkv, D, generator=g) * 0.7).to(dt)
+    v = (torch.randn(sum(lk), Hkv, D, generator=g) * 0.7).to(dt)
+    do = (torch.randn(sum(lq), Hq, D, generator=g) * 0.7).to(dt)
+    return dtype, q, k, v, do, cu_q, cu_k, max(lq), max(lk), causal, bwd
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_varlen_forward_backward(name):
+    import stackkernels_b200 as skb
+    from oracle import attention_oracle as orc
+    from stackkernels_b200 import _lib
+    from stackkernels_b200.launchers import flash_attn_fwd
+    dtype, q, k, v, do, cu_q, cu_k, msq, msk, causal, bwd = _make(CASES[name])
+    eo, el = orc.varlen_forward(q, k, v, cu_q, cu_k, causal=causal)
+    qd, kd, vd = (t.cuda().requires_grad_(bwd) for t in (q, k, v))
+    o, lse = skb.flash_attention_varlen(qd, kd, vd, cu_q.cuda(), cu_k.cuda(), msq, msk, is_causal=causal,
+                                        return_lse=True)
+    torch.cuda.synchronize()
+    assert_parity(o, eo, dtype, f"{name} O")
+    assert_parity(lse, el, dtype, f"{name} LSE")
+    # the dense kernel on each sequence alone gives the same bits
+    for b in range(len(cu_q) - 1):
+        q0, q1, k0, k1 = int(cu_q[b]), int(cu_q[b + 1]), int(cu_k[b]), int(cu_k[b + 1])
+        if q1 == q0 or k1 == k0 or q1 - q0 < 128 or k1 - k0 < 128:
+            continue                         # short sequences take the general kernel when run alone
+        ob, lb = flash_attn_fwd(qd.detach()[q0:q1].transpose(0, 1).unsqueeze(0),
+                                kd.detach()[k0:k1].transpose(0, 1).unsqueeze(0),
+                                vd.detach()[k0:k1].transpose(0, 1).unsqueeze(0), is_causal=causal)
+        assert torch.equal(ob[0].transpose(0, 1), o.detach()[q0:q1]), f"{name}: sequence {b} O differs from the dense kernel"
+        assert torch.equal(lb[0], lse[:, q0:q1]), f"{name}: sequence {b} LSE differs from the dense kernel"
+    if bwd:
+        o.backward(do.cuda())
+        torch.cuda.synchronize()
+        edq, edk, edv = orc.varlen_backward(do, q, k, v, cu_q, cu_k, causal=causal)
+        assert_parity(qd.grad, edq, dtype, f"{name} dQ")
+        assert_parity(kd.grad, edk, dtype, f"{name} dK")
+        assert_parity(vd.grad, edv, dtype, f"{name} dV")
+    assert _lib.device_status() == 0
+
+
+def test_varlen_shapes_outside_the_packed_kernels_run_per_sequence():
+    """fp32 has no packed kernel: the frontend runs the sequences one by one and stays differentiable."""
+    import stackkernels_b200 as skb
+    from oracle import attention_oracle as orc
+    g = torch.Generator().manual_seed(11)
+    lq = [40, 90]
+    cu = torch.tensor([0, 40, 130], dtype=torch.int32)
+    q, k, v, do = (torch.randn(sum(lq), 2, 64, generator=g) for _ in range(4))
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o, lse = skb.flash_attention_varlen(qd, kd, vd, cu.cuda(), cu.cuda(), 90, 90, causal=True, return_lse=True)
+    o.backward(do.cuda())
+    eo, el = orc.varlen_forward(q, k, v, cu, cu, causal=True)
+    edq, edk, edv = orc.varlen_backward(do, q, k, v, cu, cu, causal=True)
+    assert_parity(o, eo, "fp32", "fp32 varlen O")
+    assert_parity(lse, el, "fp32", "fp32 varlen LSE")
+    assert_parity(qd.grad, edq, "fp32", "fp32 varlen dQ")
+    assert_parity(kd.grad, edk, "fp32", "fp32 varlen dK")
+    assert_parity(vd.grad, edv, "fp32", "fp32 varlen dV")
