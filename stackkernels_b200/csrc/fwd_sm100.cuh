@@ -1,9 +1,13 @@
 // Prefill forward on Blackwell tensor cores (tcgen05) with TMEM accumulators and TMA-fed
 // shared-memory pipelines.  16-bit inputs, head dim 64 or 128.
 //
-// One CTA owns 256 query rows of one (batch, q head): two 128-row tiles that ping-pong on the
-// tensor core.  Warp roles (12 warps):
-//   warp 0      TMA producer: Q tiles once, then K and V tiles through 2-stage rings
+// One work item is 256 query rows of one (batch, q head): two 128-row tiles that ping-pong on the
+// tensor core.  A CTA starts with the item its block index names and then keeps taking the items of
+// CTAs that have not started yet (cluster launch control), so the loads and first score MMAs of the
+// next item overlap the epilogue of the current one and TMEM / barrier set-up is paid once per SM.
+// Warp roles (12 warps):
+//   warp 0      TMA producer: per item the Q tiles, then K and V tiles through 2-stage rings that
+//               run on across items; also asks the scheduler for the next item
 //   warp 1      MMA issuer (one lane): S_t = Q_t K^T and O_t += P_t V for t = 0,1
 //   warp 2      TMEM allocation / release
 //   warps 4-7   softmax for tile 0 (one query row per thread = one TMEM lane)
@@ -30,17 +34,21 @@ constexpr int kStages = 2;
 constexpr int kBoxBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit columns (128 B, swizzled)
 
 enum FwdBar {
-  Q_FULL = 0,    // +t
-  K_FULL = 2,    // +stage
-  K_EMPTY = 4,   // +stage
-  V_FULL = 6,    // +stage
-  V_EMPTY = 8,   // +stage
-  S_FULL = 10,   // +t   MMA -> softmax: S_t holds the scores of the current KV tile
-  P_FULL = 12,   // +t   softmax -> MMA: P_t stored (and O_t rescaled), 128 arrivals
-  O_DONE = 14,   // +t   MMA -> softmax: last PV of tile t finished
-  DRAIN = 16,
-  NUM_BARS = 17
+  Q_FULL = 0,       // +t
+  K_FULL = 2,       // +stage
+  K_EMPTY = 4,      // +stage
+  V_FULL = 6,       // +stage
+  V_EMPTY = 8,      // +stage
+  S_FULL = 10,      // +t   MMA -> softmax: S_t holds the scores of the current KV tile
+  P_FULL = 12,      // +t   softmax -> MMA: P_t stored (and O_t rescaled), 128 arrivals
+  O_DONE = 14,      // +t   MMA -> softmax: last PV of tile t finished
+  Q_EMPTY = 16,     // +t   MMA -> producer: the work item's last S_t MMA has read Q_t
+  SCHED_FULL = 18,  // +slot  scheduler answer (next work item) has landed
+  SCHED_EMPTY = 20, // +slot  every role has read the answer (10 arrivals)
+  DRAIN = 22,
+  NUM_BARS = 23
 };
+constexpr int kSchedReaders = 10;   // producer thread, MMA warp, 8 softmax warps
 
 template <int HD> constexpr int fwd_tile_bytes() { return kBoxBytes * (HD / 64); }
 template <int HD> constexpr int fwd_smem_bytes() {
@@ -73,12 +81,27 @@ __device__ long long g_trace[3 * 4096];
 #define SKB_TR(role, idx, ev) do {} while (0)
 #endif
 
+// One work item = 256 query rows (two 128-row tiles) of one (batch, q head), named by a block index of the
+// launch grid (x = query block, y = q head, z = batch).
+struct FwdItem {
+  int hq, b, hkv, row0;
+  int qoff, koff, zb;        // packed batch: row offsets of the sequence, and "batch" 0 of the tensor maps
+  int Sq, Sk, shift;         // this item's sequence lengths; shift = Sk - Sq (bottom-right causal alignment)
+  int nt0, nt1, nmax;        // KV tiles each query tile visits
+  __device__ __forceinline__ int nt(int t) const { return t == 0 ? nt0 : nt1; }
+  size_t lse_base;
+};
+
+// persist != 0: the CTA keeps going after its own work item: it asks the hardware scheduler (cluster launch
+// control) for the block index of a CTA of this grid that has not started yet and does that CTA's work, until
+// none is left.  Loads and the first score MMAs of the next item then overlap the epilogue of the current one,
+// and the launch order (heaviest causal blocks first, head-major for L2 reuse of K/V) is kept.
 template <typename T, int HD>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, T* __restrict__ o, const Strides o_str,
-           float* __restrict__ lse, const Varlen vl, int Hq, int Hkv, int Sq, int Sk, int D, int causal,
-           float scale_log2) {
+           float* __restrict__ lse, const Varlen vl, int Hq, int Hkv, int Sq_in, int Sk_in, int D, int causal,
+           float scale_log2, int persist) {
   // D <= HD is the head dimension in memory (a multiple of 8): the tensor maps are built over D columns, so
   // the bulk copies fill columns [D, HD) of every Q/K/V tile with zeros and the products are unchanged; only
   // the first D columns of O are stored.
@@ -94,46 +117,58 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const uint32_t sK = sQ + 2 * TILE;                   // kStages tiles
   const uint32_t sV = sK + kStages * TILE;             // kStages tiles
   const uint32_t sBar = sV + kStages * TILE;           // NUM_BARS x 8 bytes
+  const uint32_t sResp = sBar + 224;                   // 2 x 16-byte scheduler answers
   uint8_t* gen_base = smem_raw + (sbase - ptx::smem_u32(smem_raw));
   uint8_t* gen_misc = gen_base + (2 + 2 * kStages) * TILE + NUM_BARS * 8;
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen_misc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(gen_misc + 8);
+  static_assert(NUM_BARS * 8 + 16 <= 224, "barriers, TMEM base and abort flag must end before the scheduler answers");
   auto bar = [&](int i) -> uint32_t { return sBar + 8u * (uint32_t)i; };
 
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
 
-  const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;   // heaviest (latest) causal blocks first
-  const int hq = blockIdx.y, b = blockIdx.z;
-  const int hkv = hq / (Hq / Hkv);
-  // Packed batch: this CTA's sequence is rows [qoff, qoff+Sq) of q/o and [koff, koff+Sk) of k/v, all in "batch" 0
-  // of the tensor maps (Sq, Sk as passed in are only the grid's upper bounds).  Rows a tile reads past the end of
-  // its sequence are the next sequence's: keys are masked by the end-of-K test, queries are not stored.
-  int qoff = 0, koff = 0, zb = b;
-  if (vl.cu_q != nullptr) {
-    qoff = vl.cu_q[b];
-    Sq = vl.cu_q[b + 1] - qoff;
-    koff = vl.cu_k[b];
-    Sk = vl.cu_k[b + 1] - koff;
-    zb = 0;
-  }
-  const size_t lse_base = vl.cu_q != nullptr ? (size_t)hq * vl.total_q + qoff : ((size_t)b * Hq + hq) * Sq;
-  const int row0 = qblk * 2 * kTileM;
-  const int shift = Sk - Sq;
-
-  int ntile[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int r0 = row0 + t * kTileM;
-    int lim = Sk;
-    if (causal) lim = min(Sk, r0 + kTileM + shift);
-    ntile[t] = (r0 < Sq && lim > 0) ? cdiv(lim, kTileN) : 0;
-  }
-  const int nmax = max(ntile[0], ntile[1]);
+  // Work item named by block index (bx, by, bz).
+  auto make_item = [&](int bx, int by, int bz) -> FwdItem {
+    FwdItem I;
+    const int qblk = (int)gridDim.x - 1 - bx;          // heaviest (latest) causal blocks first
+    I.hq = by;
+    I.b = bz;
+    I.hkv = by / (Hq / Hkv);
+    I.row0 = qblk * 2 * kTileM;
+    I.qoff = 0; I.koff = 0; I.zb = bz; I.Sq = Sq_in; I.Sk = Sk_in;
+    // Packed batch: this item's sequence is rows [qoff, qoff+Sq) of q/o and [koff, koff+Sk) of k/v, all in "batch" 0
+    // of the tensor maps (Sq_in, Sk_in are only the grid's upper bounds).  Rows a tile reads past the end of its
+    // sequence are the next sequence's: keys are masked by the end-of-K test, queries are not stored.
+    if (vl.cu_q != nullptr) {
+      I.qoff = vl.cu_q[bz];
+      I.Sq = vl.cu_q[bz + 1] - I.qoff;
+      I.koff = vl.cu_k[bz];
+      I.Sk = vl.cu_k[bz + 1] - I.koff;
+      I.zb = 0;
+    }
+    I.lse_base = vl.cu_q != nullptr ? (size_t)by * vl.total_q + I.qoff : ((size_t)bz * Hq + by) * I.Sq;
+    I.shift = I.Sk - I.Sq;
+    auto tiles_of = [&](int t) -> int {
+      const int r0 = I.row0 + t * kTileM;
+      int lim = I.Sk;
+      if (causal) lim = min(I.Sk, r0 + kTileM + I.shift);
+      return (r0 < I.Sq && lim > 0) ? cdiv(lim, kTileN) : 0;
+    };
+    I.nt0 = tiles_of(0);
+    I.nt1 = tiles_of(1);
+    I.nmax = max(I.nt0, I.nt1);
+    return I;
+  };
 
   if (threadIdx.x == 0) {
     *s_abort = 0;
-    for (int i = 0; i < NUM_BARS; ++i) ptx::mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? 128u : 1u);
+    for (int i = 0; i < NUM_BARS; ++i) {
+      uint32_t count = 1u;
+      if (i == P_FULL || i == P_FULL + 1) count = 128u;
+      if (i == SCHED_EMPTY || i == SCHED_EMPTY + 1) count = (uint32_t)kSchedReaders;
+      ptx::mbar_init(bar(i), count);
+    }
     ptx::fence_mbar_init();
   }
   if (warp == 2) {
@@ -145,6 +180,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   ptx::tc_fence_after();
   const uint32_t tmem = __shfl_sync(0xffffffffu, *s_tmem, 0);
 
+  // Every role walks the same sequence of work items.  After item n it reads the scheduler's answer from slot
+  // n & 1 (requested by the producer when it started item n) and either takes the next item or stops.
+  auto next_item = [&](uint32_t n, int& bx, int& by, int& bz, bool all_lanes, bool& ok) -> bool {
+    const int sl = (int)(n & 1u);
+    ok = ptx::mbar_wait(bar(SCHED_FULL + sl), (n >> 1) & 1u, s_abort);
+    if (all_lanes) ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return false;
+    const bool valid = ptx::clc_query(sResp + 16u * sl, bx, by, bz);
+    if (all_lanes) __syncwarp();
+    if (!all_lanes || lane == 0) ptx::mbar_arrive(bar(SCHED_EMPTY + sl));
+    return valid;
+  };
+
   if (warp < 4) {
     ptx::setmaxnreg_dec<56>();
     if (warp == 0 && lane == 0) {
@@ -152,31 +200,53 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ptx::prefetch_tmap(&tm_q);
       ptx::prefetch_tmap(&tm_k);
       ptx::prefetch_tmap(&tm_v);
-      auto load_q = [&](int t) {
-        ptx::mbar_expect_tx(bar(Q_FULL + t), TILE);
-        for (int h = 0; h < HD / 64; ++h)
-          ptx::tma_load_4d(sQ + t * TILE + h * kBoxBytes, &tm_q, h * 64, qoff + row0 + t * kTileM, hq, zb, bar(Q_FULL + t));
-      };
-      auto load_kv = [&](const CUtensorMap* tm, uint32_t sdst, int full0, int j) {
-        const int st = j % kStages;
-        ptx::mbar_expect_tx(bar(full0 + st), TILE);
-        for (int h = 0; h < HD / 64; ++h)
-          ptx::tma_load_4d(sdst + st * TILE + h * kBoxBytes, tm, h * 64, koff + j * kTileN, hkv, zb, bar(full0 + st));
-      };
+      int bx = blockIdx.x, by = blockIdx.y, bz = blockIdx.z;
+      uint32_t g = 0;                 // K/V tiles loaded so far: ring position across work items
+      uint32_t qn[2] = {0, 0};        // work items so far that used Q tile t
       bool ok = true;
-      if (ntile[0] > 0) load_q(0);
-      if (nmax > 0) load_kv(&tm_k, sK, K_FULL, 0);
-      if (ntile[1] > 0) load_q(1);
-      if (nmax > 0) load_kv(&tm_v, sV, V_FULL, 0);
-      for (int j = 1; j < nmax && ok; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (uint32_t)((j / kStages) & 1) ^ 1u;
-        ok = ptx::mbar_wait(bar(K_EMPTY + st), ph, s_abort);
-        if (!ok) break;
-        load_kv(&tm_k, sK, K_FULL, j);
-        ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
-        if (!ok) break;
-        load_kv(&tm_v, sV, V_FULL, j);
+      for (uint32_t n = 0; ok; ++n) {
+        const FwdItem I = make_item(bx, by, bz);
+        if (persist) {
+          // ask for the item after this one; slot n & 1 is free once every role has read the answer of item n - 2
+          const int sl = (int)(n & 1u);
+          if (n >= 2) {
+            ok = ptx::mbar_wait(bar(SCHED_EMPTY + sl), ((n >> 1) - 1u) & 1u, s_abort);
+            if (!ok) break;
+          }
+          ptx::mbar_expect_tx(bar(SCHED_FULL + sl), 16);
+          ptx::clc_try_cancel(sResp + 16u * sl, bar(SCHED_FULL + sl));
+        }
+        auto load_q = [&](int t) -> bool {
+          // Q_t of the previous item is free once that item's last S_t MMA has completed
+          if (qn[t] > 0 && !ptx::mbar_wait(bar(Q_EMPTY + t), (qn[t] - 1u) & 1u, s_abort)) return false;
+          ++qn[t];
+          ptx::mbar_expect_tx(bar(Q_FULL + t), TILE);
+          for (int h = 0; h < HD / 64; ++h)
+            ptx::tma_load_4d(sQ + t * TILE + h * kBoxBytes, &tm_q, h * 64, I.qoff + I.row0 + t * kTileM, I.hq, I.zb,
+                             bar(Q_FULL + t));
+          return true;
+        };
+        auto load_kv = [&](const CUtensorMap* tm, uint32_t sdst, int full0, int st, int j) {
+          ptx::mbar_expect_tx(bar(full0 + st), TILE);
+          for (int h = 0; h < HD / 64; ++h)
+            ptx::tma_load_4d(sdst + st * TILE + h * kBoxBytes, tm, h * 64, I.koff + j * kTileN, I.hkv, I.zb, bar(full0 + st));
+        };
+        for (int j = 0; j < I.nmax && ok; ++j, ++g) {
+          const int st = (int)(g % kStages);
+          const uint32_t ph = ((g / kStages) & 1u) ^ 1u;
+          if (j == 0 && I.nt0 > 0) ok = load_q(0);
+          if (!ok) break;
+          ok = ptx::mbar_wait(bar(K_EMPTY + st), ph, s_abort);
+          if (!ok) break;
+          load_kv(&tm_k, sK, K_FULL, st, j);
+          if (j == 0 && I.nt1 > 0) ok = load_q(1);
+          if (!ok) break;
+          ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
+          if (!ok) break;
+          load_kv(&tm_v, sV, V_FULL, st, j);
+        }
+        if (!ok || !persist) break;
+        if (!next_item(n, bx, by, bz, false, ok)) break;
       }
       if (!ok) atomicCAS(&g_dev_status, 0u, (1u << 16));
     } else if (warp == 1) {
@@ -199,45 +269,66 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           ptx::mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
                       ptx::desc_sw128_mnmajor(sV + st * TILE + kk * 2048, kBoxBytes), IDESC_PV, (j > 0) || (kk > 0));
       };
-      if (nmax > 0) {
-        ok = ptx::mbar_wait_warp(bar(K_FULL), 0, s_abort);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (ntile[t] > 0) {
-            ok = ptx::mbar_wait_warp(bar(Q_FULL + t), 0, s_abort);
-            if (!ok) break;
-            ptx::tc_fence_after();
-            issue_qk(t, 0);
-            if (leader) ptx::mma_commit(bar(S_FULL + t));
+      int bx = blockIdx.x, by = blockIdx.y, bz = blockIdx.z;
+      uint32_t g = 0;                 // K/V tiles consumed in earlier work items
+      uint32_t sn[2] = {0, 0};        // KV tiles of query tile t in earlier items: phase of S_FULL / P_FULL
+      uint32_t on[2] = {0, 0};        // earlier items that used query tile t: phase of Q_FULL
+      for (uint32_t n = 0; ok; ++n) {
+        const FwdItem I = make_item(bx, by, bz);
+        if (I.nmax > 0) {
+          const int st0 = (int)(g % kStages);
+          ok = ptx::mbar_wait_warp(bar(K_FULL + st0), (g / kStages) & 1u, s_abort);
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (I.nt(t) > 0) {
+              ok = ptx::mbar_wait_warp(bar(Q_FULL + t), on[t] & 1u, s_abort);
+              if (!ok) break;
+              ptx::tc_fence_after();
+              // (the previous item's PV_t MMAs, which read P_t from this buffer, were issued earlier by this
+              // thread and execute in order before this overwrite)
+              issue_qk(t, st0);
+              if (leader) ptx::mma_commit(bar(S_FULL + t));
+              if (I.nt(t) == 1 && leader) ptx::mma_commit(bar(Q_EMPTY + t));
+            }
+          }
+          if (ok && leader) ptx::mma_commit(bar(K_EMPTY + st0));
+        }
+        for (int j = 0; j < I.nmax && ok; ++j) {
+          const uint32_t gj = g + (uint32_t)j, gn = gj + 1u;
+          const int st = (int)(gj % kStages), stn = (int)(gn % kStages);
+          const uint32_t ph = (gj / kStages) & 1u, phn = (gn / kStages) & 1u;
+          ok = ptx::mbar_wait_warp(bar(V_FULL + st), ph, s_abort);
+          if (leader) SKB_TR(0, j, 0);
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (j < I.nt(t)) {
+              // P_t of the item's first tile also tells that the softmax warps are done reading O_t of the
+              // previous item (same threads, program order), so PV_t may overwrite it
+              ok = ptx::mbar_wait_warp(bar(P_FULL + t), (sn[t] + (uint32_t)j) & 1u, s_abort);
+              if (!ok) break;
+              if (leader) SKB_TR(0, j, 1 + 3 * t);
+              ptx::tc_fence_after();
+              issue_pv(t, st, j);
+              if (leader) SKB_TR(0, j, 2 + 3 * t);
+              if (j == I.nt(t) - 1 && leader) ptx::mma_commit(bar(O_DONE + t));
+            }
+            if (t == 1 && leader) ptx::mma_commit(bar(V_EMPTY + st));
+            if (j + 1 < I.nt(t)) {
+              ok = ptx::mbar_wait_warp(bar(K_FULL + stn), phn, s_abort);
+              if (!ok) break;
+              ptx::tc_fence_after();
+              issue_qk(t, stn);
+              if (leader) ptx::mma_commit(bar(S_FULL + t));
+              if (j + 2 == I.nt(t) && leader) ptx::mma_commit(bar(Q_EMPTY + t));   // the item's last S_t
+              if (leader) SKB_TR(0, j, 3 + 3 * t);
+            }
+            if (t == 1 && j + 1 < I.nmax && leader) ptx::mma_commit(bar(K_EMPTY + stn));
           }
         }
-        if (ok) if (leader) ptx::mma_commit(bar(K_EMPTY));
-      }
-      for (int j = 0; j < nmax && ok; ++j) {
-        const int st = j % kStages, stn = (j + 1) % kStages;
-        const uint32_t ph = (uint32_t)(j / kStages) & 1u, phn = (uint32_t)((j + 1) / kStages) & 1u;
-        ok = ptx::mbar_wait_warp(bar(V_FULL + st), ph, s_abort);
-        if (leader) SKB_TR(0, j, 0);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j < ntile[t]) {
-            ok = ptx::mbar_wait_warp(bar(P_FULL + t), (uint32_t)j & 1u, s_abort);
-            if (!ok) break;
-            if (leader) SKB_TR(0, j, 1 + 3 * t);
-            ptx::tc_fence_after();
-            issue_pv(t, st, j);
-            if (leader) SKB_TR(0, j, 2 + 3 * t);
-            if (j == ntile[t] - 1) if (leader) ptx::mma_commit(bar(O_DONE + t));
-          }
-          if (t == 1) if (leader) ptx::mma_commit(bar(V_EMPTY + st));
-          if (j + 1 < ntile[t]) {
-            ok = ptx::mbar_wait_warp(bar(K_FULL + stn), phn, s_abort);
-            if (!ok) break;
-            ptx::tc_fence_after();
-            issue_qk(t, stn);
-            if (leader) ptx::mma_commit(bar(S_FULL + t));
-            if (leader) SKB_TR(0, j, 3 + 3 * t);
-          }
-          if (t == 1 && j + 1 < nmax) if (leader) ptx::mma_commit(bar(K_EMPTY + stn));
-        }
+        if (!ok || !persist) break;
+        g += (uint32_t)I.nmax;
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+          if (I.nt(t) > 0) { sn[t] += (uint32_t)I.nt(t); ++on[t]; }
+        if (!next_item(n, bx, by, bz, true, ok)) break;
       }
       // Drain: nothing of this CTA's tensor-core work may be in flight when TMEM is released.
       if (leader) ptx::mma_commit(bar(DRAIN));
@@ -250,17 +341,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const int t = (warp - 4) >> 2;
     const int wq = warp & 3;
     const int r = wq * 32 + lane;
-    const int grow = row0 + t * kTileM + r;
     const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
     const uint32_t tS = tmem + t_lane + t * 128;
     const uint32_t tO = tmem + t_lane + 256 + t * 128;
-    const int lim_col = causal ? min(Sk - 1, grow + shift) : Sk - 1;   // last visible key of this row
-    const int nt = ntile[t];
-    float m = -INFINITY, l = 0.f;
+    int bx = blockIdx.x, by = blockIdx.y, bz = blockIdx.z;
+    uint32_t sn = 0;                  // KV tiles of this query tile in earlier work items: phase of S_FULL
+    uint32_t on = 0;                  // earlier items that used this query tile: phase of O_DONE
     bool ok = true;
 
+   for (uint32_t n = 0; ok; ++n) {
+    const FwdItem I = make_item(bx, by, bz);
+    const int Sq = I.Sq, Sk = I.Sk;
+    const int grow = I.row0 + t * kTileM + r;
+    const int lim_col = causal ? min(Sk - 1, grow + I.shift) : Sk - 1;   // last visible key of this row
+    const int nt = I.nt(t);
+    float m = -INFINITY, l = 0.f;
+
     for (int j = 0; j < nt; ++j) {
-      ok = ptx::mbar_wait(bar(S_FULL + t), (uint32_t)j & 1u, s_abort);
+      ok = ptx::mbar_wait(bar(S_FULL + t), (sn + (uint32_t)j) & 1u, s_abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (wq == 0 && lane == 0) SKB_TR(1 + t, j, 0);
@@ -345,14 +443,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
     // ------------------------------------------------------------------ epilogue
     if (ok && nt > 0) {
-      ok = ptx::mbar_wait(bar(O_DONE + t), 0, s_abort);
+      ok = ptx::mbar_wait(bar(O_DONE + t), on & 1u, s_abort);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       ptx::tc_fence_after();
       const bool seen = (m != -INFINITY) && l > 0.f;    // false: no visible key in the whole row
       const float inv = seen ? 1.f / l : 0.f;
-      T* orow = o + o_str.at(zb, hq, qoff + max(0, min(grow, Sq - 1)));
+      T* orow = o + o_str.at(I.zb, I.hq, I.qoff + max(0, min(grow, Sq - 1)));
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t orr[32];
@@ -376,10 +474,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
       }
-      if (grow < Sq) lse[lse_base + grow] = seen ? (m + log2f(l)) * kLn2 : -INFINITY;
+      if (grow < Sq) lse[I.lse_base + grow] = seen ? (m + log2f(l)) * kLn2 : -INFINITY;
     } else if (lane == 0) {
       atomicCAS(&g_dev_status, 0u, (3u << 16) | (unsigned)warp);
     }
+    if (!ok || !persist) break;
+    sn += (uint32_t)nt;
+    if (nt > 0) ++on;
+    if (!next_item(n, bx, by, bz, true, ok)) break;
+   }
   }
 
   ptx::tc_fence_before();

@@ -212,7 +212,8 @@ bool fwd_sm100_covers(int D, int dtype, float scale) {
 template <typename T, int HD>
 int launch_fwd_sm100(const void* q, const Strides& qs, const void* k, const Strides& ks, const void* v, const Strides& vs,
                      void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Sq, int Sk, int D, int causal,
-                     float scale, cudaStream_t st, const Varlen& vl = Varlen{nullptr, nullptr, 0, 0}, int total_k = 0) {
+                     float scale, cudaStream_t st, const Varlen& vl = Varlen{nullptr, nullptr, 0, 0}, int total_k = 0,
+                     int persist = 1) {
   // packed batch: the maps cover all total_q / total_k rows as one "batch"; Sq, Sk only size the grid
   const bool packed = vl.cu_q != nullptr;
   CUtensorMap mq, mk, mv;
@@ -224,7 +225,8 @@ int launch_fwd_sm100(const void* q, const Strides& qs, const void* k, const Stri
   constexpr size_t smem = sm100::fwd_smem_bytes<HD>();
   if (int rc = set_smem(kern, smem)) return rc;
   dim3 grid(cdiv(Sq, 2 * sm100::kTileM), Hq, B);
-  kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, os, lse, vl, Hq, Hkv, Sq, Sk, D, causal, scale * kLog2e);
+  kern<<<grid, sm100::kFwdThreads, smem, st>>>(mq, mk, mv, (T*)o, os, lse, vl, Hq, Hkv, Sq, Sk, D, causal, scale * kLog2e,
+                                               persist);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -539,9 +541,13 @@ int attn_fwd_impl(const void* q, const Strides& qs, const void* k, const Strides
                      same_strides(vs, contiguous_strides(Hkv, Sk, D), B, Hkv, Sk) &&
                      same_strides(os, contiguous_strides(Hq, Sq, D), B, Hq, Sq);
   const bool covers = fwd_sm100_covers(D, dtype, scale);
-  if ((impl == SKB_IMPL_SM100 || impl == 3) && !covers) return SKB_ERR_UNSUPPORTED;
+  if ((impl == SKB_IMPL_SM100 || impl == 3 || impl == 4) && !covers) return SKB_ERR_UNSUPPORTED;
   const bool gen2 = impl == 3;   // selector for the alternative forward (Q resident in TMEM, fwd2_sm100.cuh), for A/B timing
-  if (gen2) impl = SKB_IMPL_SM100;
+  // CTAs keep taking work items (cluster launch control) unless an item is so long that its start-up and
+  // epilogue do not matter (measured on B200: +17 % at S=1024, +3 % at 4096, +1.5 % at 8192, -1 % at 16384,
+  // -2 % at 32768, where the kernel runs into the power cap either way).  Selector 4 forces one item per CTA.
+  const int persist = (impl == 4 || Sk > 12288) ? 0 : 1;
+  if (gen2 || impl == 4) impl = SKB_IMPL_SM100;
   const bool use_tc = impl == SKB_IMPL_SM100 || (impl == SKB_IMPL_AUTO && covers && Sq >= 128 && Sk >= 128);
   if (!dense) {
     // strided tensors: only the bulk-copy kernels can address them
@@ -555,7 +561,7 @@ int attn_fwd_impl(const void* q, const Strides& qs, const void* k, const Strides
     return launch_fwd2_sm100<__nv_bfloat16>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
   }
   if (use_tc) {
-#define SKB_FWD(T_, HD_) launch_fwd_sm100<T_, HD_>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st)
+#define SKB_FWD(T_, HD_) launch_fwd_sm100<T_, HD_>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st, Varlen{nullptr, nullptr, 0, 0}, 0, persist)
     if (D > 128) {
       if (dtype == SKB_F16)
         return launch_fwd_tile256<__half>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);

@@ -71,6 +71,36 @@ __device__ __forceinline__ bool elect_one() {
   return p != 0;
 }
 
+// ---------------------------------------------------------------- cluster launch control (dynamic persistence)
+// A running CTA asks the hardware scheduler for the block index of a CTA of this grid that has not started yet;
+// if it gets one, that CTA will never be launched and this one does its work.  The 16-byte answer lands in shared
+// memory and completes 16 bytes on the mbarrier.  After an answer that says "nothing left" no further request
+// may be made.
+__device__ __forceinline__ void clc_try_cancel(uint32_t response_smem, uint32_t bar) {
+  asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+               ::"r"(response_smem), "r"(bar) : "memory");
+}
+// Decode an answer: true and the block index if a CTA was cancelled in our favour.  The proxy fence orders this
+// read before the next asynchronous write to the same slot.
+__device__ __forceinline__ bool clc_query(uint32_t response_smem, int& x, int& y, int& z) {
+  uint32_t valid, bx = 0, by = 0, bz = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p1;\n\t"
+      ".reg .b128 r;\n\t"
+      "ld.shared.b128 r, [%4];\n\t"
+      "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p1, r;\n\t"
+      "selp.u32 %3, 1, 0, p1;\n\t"
+      "@p1 clusterlaunchcontrol.query_cancel.get_first_ctaid.v4.b32.b128 {%0, %1, %2, _}, r;\n\t"
+      "}"
+      : "+r"(bx), "+r"(by), "+r"(bz), "=r"(valid)
+      : "r"(response_smem)
+      : "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  x = (int)bx; y = (int)by; z = (int)bz;
+  return valid != 0;
+}
+
 // ---------------------------------------------------------------- TMA (tiled, 3-D, no multicast)
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
