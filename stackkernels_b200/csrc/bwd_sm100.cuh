@@ -86,19 +86,17 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 bwd_prep_kernel(const T* __restrict__ dout, const Strides do_str, const T* __restrict__ o, const Strides o_str,
                 const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2, int Hq, int Sq,
-                int Sq_pad, int D, size_t bh_count) {
+                int Sq_pad, int D) {
   constexpr int VE = Vec16<T>::N;
-  const size_t prow = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  // grid = (Sq_pad / 8, Hq, B): one warp per padded row
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5), ih = blockIdx.y, ib = blockIdx.z;
   const int lane = threadIdx.x & 31;
-  if (prow >= bh_count * Sq_pad) return;
-  const size_t bh = prow / Sq_pad;
-  const int r = (int)(prow % Sq_pad);
+  const size_t bh = (size_t)ib * Hq + ih;
+  const size_t prow = bh * Sq_pad + r;
   if (r >= Sq) {
     if (lane == 0) { delta[prow] = 0.f; lse2[prow] = -INFINITY; }
     return;
   }
-  const size_t row = bh * Sq + r;
-  const int ib = (int)(bh / Hq), ih = (int)(bh % Hq);
   const T* do_row = dout + do_str.at(ib, ih, r);
   const T* o_row = o + o_str.at(ib, ih, r);
   float s = 0.f;
@@ -113,7 +111,7 @@ bwd_prep_kernel(const T* __restrict__ dout, const Strides do_str, const T* __res
   for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
   if (lane == 0) {
     delta[prow] = -s;
-    const float l = lse[row];
+    const float l = lse[bh * Sq + r];
     lse2[prow] = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
   }
 }
@@ -155,20 +153,22 @@ bwd_prep_varlen_kernel(const T* __restrict__ dout, const Strides do_str, const T
   }
 }
 
-// Postprocess: dQ = T(scale * dQ_accumulator); the accumulator is (B*Hq, Sq, D) contiguous, dQ may be strided.
+// Rows of the fp32 dQ accumulator are kBwdAccStride floats apart whatever D is, so that the main kernel's
+// reductions use compile-time offsets.
+constexpr int kBwdAccStride = 128;
+
+// Postprocess: dQ = T(scale * dQ_accumulator).  grid = (rows / 8, heads, batches): one warp per row, lane i
+// converts columns [4i, 4i+4).  The accumulator is (batches, heads, rows, kBwdAccStride); dQ may be strided.
 template <typename T>
 __global__ void __launch_bounds__(256)
-bwd_post_kernel(const float* __restrict__ acc, T* __restrict__ dq, const Strides dq_str, float scale, int Hq, int Sq,
-                int D, size_t n4) {
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n4) return;
-  const float4 v = reinterpret_cast<const float4*>(acc)[i];
+bwd_post_kernel(const float* __restrict__ acc, T* __restrict__ dq, const Strides dq_str, float scale, int rows, int D) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), ih = blockIdx.y, ib = blockIdx.z;
+  const int c = (threadIdx.x & 31) * 4;
+  if (row >= rows || c >= D) return;
+  const size_t arow = ((size_t)ib * gridDim.y + ih) * rows + row;
+  const float4 v = *reinterpret_cast<const float4*>(acc + arow * kBwdAccStride + c);
   T out[4] = {from_f<T>(v.x * scale), from_f<T>(v.y * scale), from_f<T>(v.z * scale), from_f<T>(v.w * scale)};
-  const size_t e = i * 4, row = e / D;
-  const int c = (int)(e % D);
-  const size_t bh = row / Sq;
-  T* dst = dq + dq_str.at((int)(bh / Hq), (int)(bh % Hq), (long long)(row % Sq)) + c;
-  *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<uint2*>(out);
+  *reinterpret_cast<uint2*>(dq + dq_str.at(ib, ih, row) + c) = *reinterpret_cast<uint2*>(out);
 }
 
 
@@ -258,7 +258,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   // unit -> (query head, first query row)
   auto head_of = [&](int u) { return hkv * G + u / per_head; };
-  auto row_of = [&](int u) { return (s_start + u % per_head) * kBwdQ; };
+  // The CTAs of the other KV tiles of this head add into the same dQ rows.  If all of them walked the query
+  // chunks in the same order they would hit the same lines of the accumulator at the same time and the
+  // reductions would serialise in L2; each KV tile therefore starts its walk at a different chunk.
+  const int rot = per_head > 0 ? (int)(((long long)jt * per_head) / (int)gridDim.x) % per_head : 0;
+  auto row_of = [&](int u) {
+    int c = u % per_head + rot;
+    if (c >= per_head) c -= per_head;
+    return (s_start + c) * kBwdQ;
+  };
 
   if (warp < 4) {
     ptx::setmaxnreg_dec<56>();
@@ -491,14 +499,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         ptx::tmem_wait_ld();
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar(B_RP_FREE + w));
-        float* dst = dq_acc + (acc_base(head_of(u)) + q0) * D + r;
+        float* dst = dq_acc + (acc_base(head_of(u)) + q0) * kBwdAccStride + r;
         const int q_lim = r < D ? Sq - q0 : 0;       // lanes past the head dimension hold zeros: nothing to add
 #pragma unroll
         for (int c = 0; c < 32; ++c)
-          if (c < q_lim) red_add(dst + (size_t)c * D, __uint_as_float(qa[c]));
+          if (c < q_lim) red_add(dst + c * kBwdAccStride, __uint_as_float(qa[c]));
 #pragma unroll
         for (int c = 0; c < 32; ++c)
-          if (32 + c < q_lim) red_add(dst + (size_t)(32 + c) * D, __uint_as_float(qb[c]));
+          if (32 + c < q_lim) red_add(dst + (32 + c) * kBwdAccStride, __uint_as_float(qb[c]));
       }
       if (wq == 0 && lane == 0) SKB_TR(1 + w, u >> 1, 5);
     }

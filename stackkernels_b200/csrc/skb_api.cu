@@ -287,7 +287,8 @@ BwdWs bwd_sm100_ws(int B, int Hq, int Sq, int D) {
   w.delta_off = 0;
   w.lse2_off = stats;
   w.dq_off = 2 * stats;
-  w.total = 2 * stats + align_up((size_t)B * Hq * Sq * D * sizeof(float), 256);
+  (void)D;   // accumulator rows are kBwdAccStride floats whatever D is
+  w.total = 2 * stats + align_up((size_t)B * Hq * Sq * sm100::kBwdAccStride * sizeof(float), 256);
   return w;
 }
 
@@ -305,7 +306,8 @@ BwdWs bwd_varlen_ws(int B, int Hq, int total_q, int D) {
   w.delta_off = 0;
   w.lse2_off = stats;
   w.dq_off = 2 * stats;
-  w.total = 2 * stats + align_up((size_t)Hq * total_q * D * sizeof(float), 256);
+  (void)D;
+  w.total = 2 * stats + align_up((size_t)Hq * total_q * sm100::kBwdAccStride * sizeof(float), 256);
   return w;
 }
 
@@ -328,16 +330,15 @@ int launch_bwd_varlen(const BwdTensors& t, const float* lse, const int32_t* cu_q
   sm100::bwd_prep_varlen_kernel<T><<<dim3(max_pad / 8, Hq, B), 256, 0, st>>>((const T*)t.dout, t.dos, (const T*)t.o, t.os,
                                                                             lse, delta, lse2, vl, D);
   SKB_CUDA(cudaGetLastError());
-  SKB_CUDA(cudaMemsetAsync(dq_acc, 0, (size_t)Hq * total_q * D * sizeof(float), st));
+  SKB_CUDA(cudaMemsetAsync(dq_acc, 0, (size_t)Hq * total_q * sm100::kBwdAccStride * sizeof(float), st));
   auto kern = sm100::bwd_kernel<T>;
   if (int rc = set_smem(kern, sm100::kBwdSmemBytes)) return rc;
   kern<<<dim3(cdiv(max_sk, 128), Hkv, B), sm100::kBwdThreads, sm100::kBwdSmemBytes, st>>>(
       mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)t.dk, t.dks, (T*)t.dv, t.dvs, vl, Hq, Hkv, max_sq, max_sk, 0, D, causal,
       scale, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
-  // the accumulator is (Hq, total_q, D): the post kernel's (batch*head, row) with one batch of Hq heads
-  const size_t n4 = (size_t)Hq * total_q * D / 4;
-  sm100::bwd_post_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_acc, (T*)t.dq, t.dqs, scale, Hq, total_q, D, n4);
+  // the accumulator is (Hq, total_q, stride): one "batch" of Hq heads with total_q rows each
+  sm100::bwd_post_kernel<T><<<dim3(cdiv(total_q, 8), Hq, 1), 256, 0, st>>>(dq_acc, (T*)t.dq, t.dqs, scale, total_q, D);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -358,19 +359,17 @@ int launch_bwd_sm100(const BwdTensors& t, const float* lse, int B, int Hq, int H
   if (int rc = make_map_4d(&mk, dt, t.k, D, Sk, Hkv, B, t.ks)) return rc;
   if (int rc = make_map_4d(&mv, dt, t.v, D, Sk, Hkv, B, t.vs)) return rc;
 
-  const size_t prows = bh * sq_pad;
-  sm100::bwd_prep_kernel<T><<<(unsigned)((prows + 7) / 8), 256, 0, st>>>((const T*)t.dout, t.dos, (const T*)t.o, t.os, lse,
-                                                                        delta, lse2, Hq, Sq, sq_pad, D, bh);
+  sm100::bwd_prep_kernel<T><<<dim3(sq_pad / 8, Hq, B), 256, 0, st>>>((const T*)t.dout, t.dos, (const T*)t.o, t.os, lse, delta,
+                                                                    lse2, Hq, Sq, sq_pad, D);
   SKB_CUDA(cudaGetLastError());
-  SKB_CUDA(cudaMemsetAsync(dq_acc, 0, bh * Sq * D * sizeof(float), st));
+  SKB_CUDA(cudaMemsetAsync(dq_acc, 0, bh * Sq * sm100::kBwdAccStride * sizeof(float), st));
   auto kern = sm100::bwd_kernel<T>;
   if (int rc = set_smem(kern, sm100::kBwdSmemBytes)) return rc;
   kern<<<dim3(cdiv(Sk, 128), Hkv, B), sm100::kBwdThreads, sm100::kBwdSmemBytes, st>>>(
       mq, mk, mv, mdo, lse2, delta, dq_acc, (T*)t.dk, t.dks, (T*)t.dv, t.dvs, Varlen{nullptr, nullptr, 0, 0}, Hq, Hkv, Sq,
       Sk, sq_pad, D, causal, scale, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
-  const size_t n4 = bh * Sq * D / 4;
-  sm100::bwd_post_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dq_acc, (T*)t.dq, t.dqs, scale, Hq, Sq, D, n4);
+  sm100::bwd_post_kernel<T><<<dim3(cdiv(Sq, 8), Hq, B), 256, 0, st>>>(dq_acc, (T*)t.dq, t.dqs, scale, Sq, D);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
