@@ -46,8 +46,8 @@ DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel per launch, from the ncu
 # captures summarised under profiles/ (taken on a smaller case of the same kernel and scaled by the units).
 NCU_TRAFFIC_BYTES = {
-    "prefill_fwd_c2": 4 * 251.0e6,        # profiles/fwd_sm100_prefill_bf16_d128.md
-    "prefill_fwd_profile": 251.0e6,
+    "prefill_fwd_c2": 4 * 254.5e6,        # profiles/fwd_sm100_prefill_bf16_d128.md
+    "prefill_fwd_profile": 254.5e6,
     "fwdbwd_c3": 4 * 1136.6e6,            # profiles/bwd_sm100_bf16_d128.md
     "bwd_profile": 1136.6e6,
     "decode_c4": 8 * 855.5e6,             # profiles/decode_group_bf16_d128.md
