@@ -64,6 +64,52 @@ def test_argument_validation_happens_on_host(lib):
     assert rc == _lib.SKB_ERR_TOO_LARGE
 
 
+def test_strided_paged_varlen_entry_points_validate_on_host(lib):
+    """The newer entry points reject what they cannot run before touching the device."""
+    p = ctypes.c_void_p(1 << 20)   # never dereferenced
+    i64x3 = ctypes.c_int64 * 3
+    dense_q = i64x3(4 * 256 * 128, 256 * 128, 128)      # (B, Hq=4, S=256, D=128) contiguous
+    dense_k = i64x3(2 * 256 * 128, 256 * 128, 128)
+    bshd_q = i64x3(256 * 4 * 128, 128, 4 * 128)         # the same tensor stored (B, S, H, D)
+    bshd_k = i64x3(256 * 2 * 128, 128, 2 * 128)
+    odd = i64x3(256 * 4 * 128 + 4, 128, 4 * 128)        # batch stride not a multiple of 8 elements
+
+    def fwd_s(qs, ks, dt=_lib.SKB_BF16, B=2, impl=0):
+        return lib.skb_attn_fwd_strided(p, qs, p, ks, p, ks, p, qs, p, B, 4, 2, 256, 256, 128, dt, 1, 0.1, impl, None)
+    assert fwd_s(None, dense_k) == _lib.SKB_ERR_NULL
+    assert fwd_s(bshd_q, bshd_k, dt=_lib.SKB_F32) == _lib.SKB_ERR_UNSUPPORTED     # fp32: general kernels need dense
+    assert fwd_s(bshd_q, bshd_k, impl=_lib.IMPL_GENERAL) == _lib.SKB_ERR_UNSUPPORTED
+    assert fwd_s(odd, bshd_k) == _lib.SKB_ERR_ALIGN
+    # paged decode: page size must be a power of two >= 8; fp32 has no group kernel
+    pg = i64x3(2 * 16 * 64, 16 * 64, 64)
+    qd = i64x3(4 * 64, 64, 64)
+
+    def paged(page=16, dt=_lib.SKB_F16, table=p, lens=p):
+        return lib.skb_decode_paged(p, qd, p, pg, p, pg, table, 8, lens, p, qd, None, 2, 4, 2, 32, page, 64, dt, 0.125,
+                                    1, p, 1 << 20, None)
+    assert paged(page=12) == _lib.SKB_ERR_SHAPE
+    assert paged(page=4) == _lib.SKB_ERR_SHAPE
+    assert paged(table=None) == _lib.SKB_ERR_NULL
+    assert paged(lens=None) == _lib.SKB_ERR_NULL
+    assert paged(dt=_lib.SKB_F32) == _lib.SKB_ERR_UNSUPPORTED
+    # packed batches: bounds of max_seqlen, dtype coverage, workspace
+    i64x2 = ctypes.c_int64 * 3
+    ps = i64x2(4 * 128, 128, 0)
+    ks = i64x2(2 * 128, 128, 0)
+
+    def varlen(total_q=512, max_sq=256, dt=_lib.SKB_BF16, D=128):
+        return lib.skb_attn_fwd_varlen(p, ps, p, ks, p, ks, p, ps, p, p, p, 2, 4, 2, total_q, 512, max_sq, 256, D, dt, 1,
+                                       0.1, None)
+    assert varlen(max_sq=1024) == _lib.SKB_ERR_SHAPE          # longer than the whole packed tensor
+    assert varlen(dt=_lib.SKB_F32) == _lib.SKB_ERR_UNSUPPORTED
+    assert varlen(D=264) == _lib.SKB_ERR_HEAD_DIM
+    need = lib.skb_attn_bwd_varlen_workspace_bytes(2, 4, 512, 128)
+    assert need >= 4 * 512 * 128 * 4 + 2 * 4 * 512 * 4
+    rc = lib.skb_attn_bwd_varlen(p, ps, p, ps, p, ks, p, ks, p, ps, p, p, ps, p, ks, p, ks, p, p, 2, 4, 2, 512, 512, 256,
+                                 256, 128, _lib.SKB_BF16, 1, 0.1, p, need - 1, None)
+    assert rc == _lib.SKB_ERR_WORKSPACE
+
+
 def test_split_scheduler_and_workspace_sizes(lib):
     # config 4 (B64 Hq32 Hkv8 cap 32768) and config 5 (B16 Hq64 Hkv1 131072)
     s4 = lib.skb_decode_num_splits(64, 32, 8, 32768, 128, _lib.SKB_BF16, 148)
