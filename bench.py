@@ -39,6 +39,9 @@ WORKLOADS = {
     "rope_c3": ("rope", dict(B=4, H=64, S=8192, D=128, dtype="bf16", seed=2)),
     "decode_c4": ("decode", dict(B=64, Hq=32, Hkv=8, cap=32768, D=128, dtype="bf16", seed=3, lens="uniform")),
     "decode_c5": ("decode", dict(B=16, Hq=64, Hkv=1, cap=131072, D=128, dtype="fp16", seed=4, lens="full", std=0.5)),
+    # head dimension 256: the one-tile tcgen05 kernel in prefill and in decode mode (profiles/tile_kernel_d256.md)
+    "prefill_fwd_d256": ("fwd", dict(B=2, Hq=32, Hkv=8, S=4096, D=256, dtype="bf16", seed=5)),
+    "decode_d256": ("decode", dict(B=16, Hq=32, Hkv=8, cap=16384, D=256, dtype="bf16", seed=6, lens="uniform")),
 }
 DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 
