@@ -88,31 +88,59 @@ bwd_prep_kernel(const T* __restrict__ dout, const Strides do_str, const T* __res
                 const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2, int Hq, int Sq,
                 int Sq_pad, int D) {
   constexpr int VE = Vec16<T>::N;
-  // grid = (Sq_pad / 8, Hq, B): one warp per padded row
-  const int r = blockIdx.x * 8 + (threadIdx.x >> 5), ih = blockIdx.y, ib = blockIdx.z;
-  const int lane = threadIdx.x & 31;
+  // grid = (Sq_pad / 64, Hq, B).  A row is D / VE 16-byte vectors; a warp takes as many whole rows as fit its 32
+  // lanes (2 at D = 128 in 16 bits) and every thread issues the loads of two rows' vectors before it sums, so
+  // that enough bytes are in flight for this pure-bandwidth pass.
+  const int vpr = D / VE;                              // vectors per row (1 .. 32)
+  const int rpw = 32 / vpr;                            // rows per warp and pass
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / vpr, c = (lane % vpr) * VE;   // row within the pass, first column of this lane's vector
+  const int ih = blockIdx.y, ib = blockIdx.z;
   const size_t bh = (size_t)ib * Hq + ih;
-  const size_t prow = bh * Sq_pad + r;
-  if (r >= Sq) {
-    if (lane == 0) { delta[prow] = 0.f; lse2[prow] = -INFINITY; }
-    return;
-  }
-  const T* do_row = dout + do_str.at(ib, ih, r);
-  const T* o_row = o + o_str.at(ib, ih, r);
-  float s = 0.f;
-  for (int c = lane * VE; c < D; c += 32 * VE) {
-    float a[VE], b2[VE];
-    load_vec16<T>(do_row + c, a);
-    load_vec16<T>(o_row + c, b2);
+  const int row0 = blockIdx.x * 64;
+  // rows of this CTA: 64; warp w takes rows row0 + w*8 .. +8 in passes of rpw rows, two passes at a time
+  for (int base = 0; base < 8; base += 2 * rpw) {
+    int r[2];
+    float s[2] = {0.f, 0.f};
+    float a[2][VE], b2[2][VE];
+    bool live[2];
 #pragma unroll
-    for (int i = 0; i < VE; ++i) s += a[i] * b2[i];
-  }
+    for (int k = 0; k < 2; ++k) {
+      const int in_warp = base + k * rpw + sub;        // 0 .. 7 when live
+      r[k] = row0 + warp * 8 + in_warp;
+      live[k] = sub < rpw && in_warp < 8 && r[k] < Sq;
+      if (live[k]) {
+        load_vec16<T>(dout + do_str.at(ib, ih, r[k]) + c, a[k]);
+        load_vec16<T>(o + o_str.at(ib, ih, r[k]) + c, b2[k]);
+      }
+    }
 #pragma unroll
-  for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) {
-    delta[prow] = -s;
-    const float l = lse[bh * Sq + r];
-    lse2[prow] = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
+    for (int k = 0; k < 2; ++k) {
+      if (live[k]) {
+#pragma unroll
+        for (int i = 0; i < VE; ++i) s[k] += a[k][i] * b2[k][i];
+      }
+      // sum over the vpr lanes of the row: lanes [sub*vpr, sub*vpr + vpr)
+      for (int off = 1; off < vpr; off <<= 1) {
+        const float other = __shfl_down_sync(0xffffffffu, s[k], off);
+        if ((lane % vpr) + off < vpr && (((lane % vpr) & (2 * off - 1)) == 0)) s[k] += other;
+      }
+      const int in_warp = base + k * rpw + sub;
+      if (sub < rpw && in_warp < 8 && (lane % vpr) == 0) {
+        const int rr = row0 + warp * 8 + in_warp;
+        if (rr < Sq_pad) {
+          const size_t prow = bh * Sq_pad + rr;
+          if (rr < Sq) {
+            delta[prow] = -s[k];
+            const float l = lse[bh * Sq + rr];
+            lse2[prow] = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
+          } else {
+            delta[prow] = 0.f;
+            lse2[prow] = -INFINITY;
+          }
+        }
+      }
+    }
   }
 }
 

@@ -359,7 +359,7 @@ int launch_bwd_sm100(const BwdTensors& t, const float* lse, int B, int Hq, int H
   if (int rc = make_map_4d(&mk, dt, t.k, D, Sk, Hkv, B, t.ks)) return rc;
   if (int rc = make_map_4d(&mv, dt, t.v, D, Sk, Hkv, B, t.vs)) return rc;
 
-  sm100::bwd_prep_kernel<T><<<dim3(sq_pad / 8, Hq, B), 256, 0, st>>>((const T*)t.dout, t.dos, (const T*)t.o, t.os, lse, delta,
+  sm100::bwd_prep_kernel<T><<<dim3(cdiv(sq_pad, 64), Hq, B), 256, 0, st>>>((const T*)t.dout, t.dos, (const T*)t.o, t.os, lse, delta,
                                                                     lse2, Hq, Sq, sq_pad, D);
   SKB_CUDA(cudaGetLastError());
   SKB_CUDA(cudaMemsetAsync(dq_acc, 0, bh * Sq * sm100::kBwdAccStride * sizeof(float), st));
