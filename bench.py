@@ -42,6 +42,9 @@ WORKLOADS = {
     # head dimension 256: the one-tile tcgen05 kernel in prefill and in decode mode (profiles/tile_kernel_d256.md)
     "prefill_fwd_d256": ("fwd", dict(B=2, Hq=32, Hkv=8, S=4096, D=256, dtype="bf16", seed=5)),
     "decode_d256": ("decode", dict(B=16, Hq=32, Hkv=8, cap=16384, D=256, dtype="bf16", seed=6, lens="uniform")),
+    # fp32 tensors through the tensor cores as TF32 (opt-in), and the same shape on the default exact fp32 kernels
+    "prefill_fwd_fp32_tf32": ("fwd", dict(B=2, Hq=32, Hkv=8, S=4096, D=128, dtype="fp32", seed=7, impl="sm100")),
+    "prefill_fwd_fp32_exact": ("fwd", dict(B=2, Hq=32, Hkv=8, S=4096, D=128, dtype="fp32", seed=7)),
 }
 DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 
@@ -213,7 +216,7 @@ def run_native(args):
             cos, sin = precompute_freqs(p["D"], p["S"], device=dev)
             fn = lambda: rope_launch(d[0], cos, sin, 0)
         elif kind == "fwd":
-            fn = lambda: flash_attn_fwd(d[0], d[1], d[2], is_causal=True)
+            fn = lambda: flash_attn_fwd(d[0], d[1], d[2], is_causal=True, impl=p.get("impl", "auto"))
         elif kind == "bwd":
             o, lse = flash_attn_fwd(d[0], d[1], d[2], is_causal=True)
             fn = lambda: flash_attn_bwd(d[3], d[0], d[1], d[2], o, lse, is_causal=True)

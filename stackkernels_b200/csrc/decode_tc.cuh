@@ -1,6 +1,6 @@
 // One-tile attention on tcgen05 tensor cores: split-KV decode for wide GQA/MQA groups, and prefill forward for
 // head dimensions the two-tile kernel of fwd_sm100.cuh has no tensor memory for (16-bit, tiles of 128 or 256
-// columns).
+// columns), and for fp32 tensors, whose operands the tensor cores take as TF32 (tiles of 128 columns).
 //
 // Decode (PREFILL = false).  With G query heads per KV head the decode step needs G FLOP per KV byte; at G = 64
 // that is more than warp-level mma.sync and its ldmatrix traffic sustain (decode_group.cuh becomes compute
@@ -28,11 +28,17 @@ using sm100::pack2;
 
 constexpr int kThreads = 256;
 
-template <int HD> struct Cfg {
-  static constexpr int kKvRows = HD == 128 ? 128 : 64;          // KV rows per tile
-  static constexpr int kStages = HD == 128 ? 3 : 2;
-  static constexpr int kQBytes = 128 * HD * 2;                  // Q tile: 128 rows
-  static constexpr int kKvBytes = kKvRows * HD * 2;             // one K or V tile
+// The tile shapes follow the bytes per row, HD * sizeof(T): 256 bytes (16-bit HD = 128, fp32 HD = 64): 128-row K/V
+// tiles, 3 stages; 512 bytes (16-bit HD = 256, fp32 HD = 128): 64-row tiles, 2 stages.
+template <typename T, int HD> struct Cfg {
+  static constexpr int kRowBytes = HD * (int)sizeof(T);
+  static_assert(kRowBytes == 256 || kRowBytes == 512, "tile rows are 256 or 512 bytes");
+  static constexpr int kBoxes = kRowBytes / 128;                // 128-byte (swizzle-width) column boxes per row
+  static constexpr int kBoxElems = 128 / (int)sizeof(T);        // elements per box row
+  static constexpr int kKvRows = kRowBytes == 256 ? 128 : 64;   // KV rows per tile
+  static constexpr int kStages = kRowBytes == 256 ? 3 : 2;
+  static constexpr int kQBytes = 128 * kRowBytes;               // Q tile: 128 rows
+  static constexpr int kKvBytes = kKvRows * kRowBytes;          // one K or V tile
   static constexpr int kKvBox = kKvRows * 128;                  // one 64-column box of a K/V tile
   static constexpr int kSmemBytes = 1024 + kQBytes + 2 * kStages * kKvBytes + 256;
 };
@@ -73,7 +79,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
             const __grid_constant__ CUtensorMap tm_v, const DecodeArgs dec, const PrefillArgs<T> pre, int Hq, int Hkv,
             int Sk, int D, float scale_log2) {
-  using C = Cfg<HD>;
+  using C = Cfg<T, HD>;
+  constexpr bool TF32 = sizeof(T) == 4;         // fp32 operands go through the tensor cores as TF32
+  constexpr int KSTEP = 32 / (int)sizeof(T);     // elements of the contraction per MMA instruction (32 bytes)
   constexpr int KV = C::kKvRows, STAGES = C::kStages;
   constexpr uint32_t IDESC_QK = ptx::idesc_f16(Fmt<T>::v, 128, KV, 0, 0);
   constexpr uint32_t IDESC_PV = ptx::idesc_f16(Fmt<T>::v, 128, HD, 0, 1);
@@ -143,11 +151,11 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     if (lane == 0 && nt > 0) {
       ptx::prefetch_tmap(&tm_q); ptx::prefetch_tmap(&tm_k); ptx::prefetch_tmap(&tm_v);
       ptx::mbar_expect_tx(bar(Q_FULL), C::kQBytes);
-      for (int h = 0; h < HD / 64; ++h) {
+      for (int h = 0; h < C::kBoxes; ++h) {
         if (PREFILL)   // rows = query positions of head hq (q as {D, Sq, Hq, B})
-          ptx::tma_load_4d(sQ + h * kBoxBytes, &tm_q, h * 64, qoff + q0, hq, zb, bar(Q_FULL));
+          ptx::tma_load_4d(sQ + h * kBoxBytes, &tm_q, h * C::kBoxElems, qoff + q0, hq, zb, bar(Q_FULL));
         else           // rows = query heads of this group (q as {D, Hq, B}); rows >= G: other heads or zero fill
-          ptx::tma_load_3d(sQ + h * kBoxBytes, &tm_q, h * 64, hkv * G, b, bar(Q_FULL));
+          ptx::tma_load_3d(sQ + h * kBoxBytes, &tm_q, h * C::kBoxElems, hkv * G, b, bar(Q_FULL));
       }
     }
     if (!paged) {
@@ -161,13 +169,13 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           ok = ptx::mbar_wait(bar(K_EMPTY + st), ph, s_abort);
           if (!ok) break;
           ptx::mbar_expect_tx(bar(K_FULL + st), C::kKvBytes);
-          for (int h = 0; h < HD / 64; ++h)
-            ptx::tma_load_4d(sK(st) + h * C::kKvBox, &tm_k, h * 64, koff + row, hkv, zb, bar(K_FULL + st));
+          for (int h = 0; h < C::kBoxes; ++h)
+            ptx::tma_load_4d(sK(st) + h * C::kKvBox, &tm_k, h * C::kBoxElems, koff + row, hkv, zb, bar(K_FULL + st));
           ok = ptx::mbar_wait(bar(V_EMPTY + st), ph, s_abort);
           if (!ok) break;
           ptx::mbar_expect_tx(bar(V_FULL + st), C::kKvBytes);
-          for (int h = 0; h < HD / 64; ++h)
-            ptx::tma_load_4d(sV(st) + h * C::kKvBox, &tm_v, h * 64, koff + row, hkv, zb, bar(V_FULL + st));
+          for (int h = 0; h < C::kBoxes; ++h)
+            ptx::tma_load_4d(sV(st) + h * C::kKvBox, &tm_v, h * C::kBoxElems, koff + row, hkv, zb, bar(V_FULL + st));
         }
         if (!ok) atomicCAS(&g_dev_status, 0u, (13u << 16));
       }
@@ -193,15 +201,15 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (lane == 0) ptx::mbar_expect_tx(bar(K_FULL + st), C::kKvBytes);
         __syncwarp();
         if (lane < nsub)
-          for (int h = 0; h < HD / 64; ++h)
-            ptx::tma_load_4d(sK(st) + h * C::kKvBox + lane * sub_rows * 128, &tm_k, h * 64, prow, hkv, page, bar(K_FULL + st));
+          for (int h = 0; h < C::kBoxes; ++h)
+            ptx::tma_load_4d(sK(st) + h * C::kKvBox + lane * sub_rows * 128, &tm_k, h * C::kBoxElems, prow, hkv, page, bar(K_FULL + st));
         ok = ptx::mbar_wait_warp(bar(V_EMPTY + st), ph, s_abort);
         if (!ok) break;
         if (lane == 0) ptx::mbar_expect_tx(bar(V_FULL + st), C::kKvBytes);
         __syncwarp();
         if (lane < nsub)
-          for (int h = 0; h < HD / 64; ++h)
-            ptx::tma_load_4d(sV(st) + h * C::kKvBox + lane * sub_rows * 128, &tm_v, h * 64, prow, hkv, page, bar(V_FULL + st));
+          for (int h = 0; h < C::kBoxes; ++h)
+            ptx::tma_load_4d(sV(st) + h * C::kKvBox + lane * sub_rows * 128, &tm_v, h * C::kBoxElems, prow, hkv, page, bar(V_FULL + st));
       }
       if (!ok && lane == 0) atomicCAS(&g_dev_status, 0u, (13u << 16));
     }
@@ -213,10 +221,12 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       const uint32_t k = sK(j % STAGES);
       if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {      // K-major: 32 bytes per k-step, next 64-column box after 4
+        for (int kk = 0; kk < HD / KSTEP; ++kk) {   // K-major: 32 bytes per k-step, next 128-byte box after 4
           const uint32_t in_row = (uint32_t)(kk & 3) * 32u;
-          ptx::mma_ss(tS(j & 1), ptx::desc_sw128_kmajor(sQ + (uint32_t)(kk >> 2) * kBoxBytes + in_row),
-                      ptx::desc_sw128_kmajor(k + (uint32_t)(kk >> 2) * C::kKvBox + in_row), IDESC_QK, kk > 0);
+          const uint64_t da = ptx::desc_sw128_kmajor(sQ + (uint32_t)(kk >> 2) * kBoxBytes + in_row);
+          const uint64_t db = ptx::desc_sw128_kmajor(k + (uint32_t)(kk >> 2) * C::kKvBox + in_row);
+          if (TF32) ptx::mma_ss_tf32(tS(j & 1), da, db, IDESC_QK, kk > 0);
+          else ptx::mma_ss(tS(j & 1), da, db, IDESC_QK, kk > 0);
         }
         ptx::mma_commit(bar(S_FULL + (j & 1)));
         ptx::mma_commit(bar(K_EMPTY + j % STAGES));
@@ -240,9 +250,13 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       ptx::tc_fence_after();
       if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < KV / 16; ++kk)        // MN-major V: 16 rows (2048 bytes) per k-step, boxes kKvBox apart
-          ptx::mma_ts(tO, tS(buf) + kk * 8, ptx::desc_sw128_mnmajor(sV(st) + kk * 2048, C::kKvBox), IDESC_PV,
-                      (j > 0) || (kk > 0));
+        for (int kk = 0; kk < KV / KSTEP; ++kk) {   // MN-major V: KSTEP rows of 128 bytes per k-step, boxes kKvBox apart;
+          // P: KSTEP values = 8 TMEM columns per k-step (two 16-bit values or one TF32 value per column)
+          const uint64_t dv = TF32 ? ptx::desc_sw128_atom32_mnmajor(sV(st) + kk * KSTEP * 128, C::kKvBox)
+                                   : ptx::desc_sw128_mnmajor(sV(st) + kk * KSTEP * 128, C::kKvBox);
+          if (TF32) ptx::mma_ts_tf32(tO, tS(buf) + kk * 8, dv, IDESC_PV, (j > 0) || (kk > 0));
+          else ptx::mma_ts(tO, tS(buf) + kk * 8, dv, IDESC_PV, (j > 0) || (kk > 0));
+        }
         ptx::mma_commit(bar(V_EMPTY + st));
         ptx::mma_commit(bar(O_READY));
       }
@@ -284,7 +298,7 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (r >= tile_rows && r < KV) {
           uint8_t* vrow = gbase + (sV(st) - sbase) + r * 128;
 #pragma unroll
-          for (int h = 0; h < HD / 64; ++h)
+          for (int h = 0; h < C::kBoxes; ++h)
 #pragma unroll
             for (int c = 0; c < 8; ++c)
               *reinterpret_cast<uint4*>(vrow + h * C::kKvBox + c * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -320,6 +334,16 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
         for (int e = 0; e < 6; ++e) pe[e] = ptx::ex2(x[e]);
         ptx::exp2_poly2(x[6], x[7], pe[6], pe[7]);
+        if constexpr (TF32) {
+          // round P to TF32 here (the MMA would truncate it) and sum the rounded values, so that numerator and
+          // denominator of the softmax use the same probabilities and the truncation bias (-2^-11) disappears
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            uint32_t rbits;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(rbits) : "f"(pe[e]));
+            pe[e] = __uint_as_float(rbits);
+          }
+        }
         if (valid < KV) {                          // polynomial exponentials of -inf are tiny, not zero
 #pragma unroll
           for (int e = 0; e < 8; ++e)
@@ -328,7 +352,14 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         sumA = ptx::f2_add(sumA, ptx::f2_add(ptx::f2_pack(pe[0], pe[1]), ptx::f2_pack(pe[2], pe[3])));
         sumB = ptx::f2_add(sumB, ptx::f2_add(ptx::f2_pack(pe[4], pe[5]), ptx::f2_pack(pe[6], pe[7])));
 #pragma unroll
-        for (int e = 0; e < 8; e += 2) sr[(c + e) >> 1] = pack2(pe[e], pe[e + 1], T());
+        for (int e = 0; e < 8; e += 2) {
+          if constexpr (TF32) {                    // P as fp32 bits, one value per TMEM column (used as TF32)
+            sr[c + e] = __float_as_uint(pe[e]);
+            sr[c + e + 1] = __float_as_uint(pe[e + 1]);
+          } else {                                 // P as 16-bit pairs, two values per TMEM column
+            sr[(c + e) >> 1] = pack2(pe[e], pe[e + 1], T());
+          }
+        }
       }
       {
         float a0, a1, b0, b1;
@@ -337,7 +368,7 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         l += (a0 + a1) + (b0 + b1);
       }
 #pragma unroll
-      for (int c = 0; c < KV / 64; ++c) ptx::tmem_st32(tS(buf) + t_lane + c * 32, sr + c * 32);
+      for (int c = 0; c < (TF32 ? KV / 32 : KV / 64); ++c) ptx::tmem_st32(tS(buf) + t_lane + c * 32, sr + c * 32);
       if (j > 0 && __any_sync(0xffffffffu, grow_m)) {
         // PV of tile j-1 finished?  (S_FULL of tile j implies PV of tile j-2 finished, so the barrier is at most
         // one phase behind and the parity wait cannot return early.)
@@ -385,12 +416,22 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               if (c * 32 + i >= D) break;
-              uint4 w;
-              w.x = pack2(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv, T());
-              w.y = pack2(__uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv, T());
-              w.z = pack2(__uint_as_float(orr[i + 4]) * inv, __uint_as_float(orr[i + 5]) * inv, T());
-              w.w = pack2(__uint_as_float(orr[i + 6]) * inv, __uint_as_float(orr[i + 7]) * inv, T());
-              *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+              if constexpr (TF32) {
+                *reinterpret_cast<float4*>(orow + c * 32 + i) =
+                    make_float4(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv,
+                                __uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv);
+                if (c * 32 + i + 4 < D)
+                  *reinterpret_cast<float4*>(orow + c * 32 + i + 4) =
+                      make_float4(__uint_as_float(orr[i + 4]) * inv, __uint_as_float(orr[i + 5]) * inv,
+                                  __uint_as_float(orr[i + 6]) * inv, __uint_as_float(orr[i + 7]) * inv);
+              } else {
+                uint4 w;
+                w.x = pack2(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv, T());
+                w.y = pack2(__uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv, T());
+                w.z = pack2(__uint_as_float(orr[i + 4]) * inv, __uint_as_float(orr[i + 5]) * inv, T());
+                w.w = pack2(__uint_as_float(orr[i + 6]) * inv, __uint_as_float(orr[i + 7]) * inv, T());
+                *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+              }
             }
           }
         }

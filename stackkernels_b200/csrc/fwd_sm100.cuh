@@ -58,6 +58,7 @@ template <int HD> constexpr int fwd_smem_bytes() {
 template <typename T> struct Fmt;
 template <> struct Fmt<__half> { static constexpr int v = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
+template <> struct Fmt<float> { static constexpr int v = 2; };   // fp32 operands used as TF32 (kind::tf32)
 
 __device__ __forceinline__ uint32_t pack2(float a, float b, __half) {
   __half2 h = __floats2half2_rn(a, b);

@@ -153,7 +153,7 @@ EncodeTiledFn get_encode_tiled() {
 // thread.  A thread that has only inherited a device ordinal (e.g. an autograd worker) may not have it
 // bound yet; cudaSetDevice on the current ordinal binds it.
 int encode_map(CUtensorMap* map, int dtype, const void* ptr, int rank, const cuuint64_t* dims,
-               const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+               const cuuint64_t* strides_bytes, const cuuint32_t* box, bool atom32 = false) {
   int dev = 0;
   SKB_CUDA(cudaGetDevice(&dev));
   SKB_CUDA(cudaSetDevice(dev));
@@ -163,9 +163,15 @@ int encode_map(CUtensorMap* map, int dtype, const void* ptr, int rank, const cuu
     return SKB_ERR_CUDA;
   }
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(map, dtype == SKB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+  // fp32 tensors are fetched as TF32: the copy engine rounds them for the tensor cores on the way in
+  const CUtensorMapDataType type = dtype == SKB_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                   : dtype == SKB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                       : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32;
+  CUresult r = enc(map, type,
                    (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides_bytes, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     snprintf(tl_cuda_err, sizeof(tl_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -176,27 +182,30 @@ int encode_map(CUtensorMap* map, int dtype, const void* ptr, int rank, const cuu
 
 // (B, H, S, D) 16-bit tensor with element strides `str` (D contiguous) as a 4-D map {D, S, H, B}: boxes of
 // 64 columns x box_rows rows, 128-byte swizzle, out-of-range rows and columns read as zero.
+// atom32: the 128-byte swizzle with 32-byte atoms, which an MN-major 32-bit MMA operand (V of an fp32 problem) needs.
 int make_map_4d(CUtensorMap* map, int dtype, const void* ptr, int D, int S, int H, int B, const Strides& str,
-                int box_rows = 128) {
+                int box_rows = 128, bool atom32 = false) {
   const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  const int es = dtype == SKB_F32 ? 4 : 2;
   // a dimension of extent 1 is never stepped over; give it a harmless legal stride
-  auto sb = [&](long long e, int extent) { return (cuuint64_t)((extent > 1 ? e : (long long)D) * 2); };
+  auto sb = [&](long long e, int extent) { return (cuuint64_t)((extent > 1 ? e : (long long)D) * es); };
   const cuuint64_t strides[3] = {sb(str.s, S), sb(str.h, H), sb(str.b, B)};
-  const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
-  return encode_map(map, dtype, ptr, 4, dims, strides, box);
+  const cuuint32_t box[4] = {(cuuint32_t)(128 / es), (cuuint32_t)box_rows, 1, 1};   // 128-byte rows
+  return encode_map(map, dtype, ptr, 4, dims, strides, box, atom32);
 }
 
 // Decode queries (B, Hq, 1, D) as a 3-D map {D, Hq, B}: one box = the 128 heads from a given head on.
 int make_map_q_heads(CUtensorMap* map, int dtype, const void* ptr, int D, int Hq, int B, const Strides& str) {
   const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Hq, (cuuint64_t)B};
-  const cuuint64_t strides[2] = {(cuuint64_t)((Hq > 1 ? str.h : (long long)D) * 2),
-                                 (cuuint64_t)((B > 1 ? str.b : (long long)D) * 2)};
-  const cuuint32_t box[3] = {64, 128, 1};
+  const int es = dtype == SKB_F32 ? 4 : 2;
+  const cuuint64_t strides[2] = {(cuuint64_t)((Hq > 1 ? str.h : (long long)D) * es),
+                                 (cuuint64_t)((B > 1 ? str.b : (long long)D) * es)};
+  const cuuint32_t box[3] = {(cuuint32_t)(128 / es), 128, 1};
   return encode_map(map, dtype, ptr, 3, dims, strides, box);
 }
 
 // What the bulk-copy engine and the 16-byte vector stores need from a strided 16-bit tensor.
-bool strides_ok(const void* p, const Strides& s, int B, int H, int S) {
+bool strides_ok(const void* p, const Strides& s, int B, int H, int S) {   // 16-bit tensors (fp32 needs only multiples of 4)
   if (!aligned16(p)) return false;
   if ((B > 1 && (s.b <= 0 || s.b % 8 != 0)) || (H > 1 && (s.h <= 0 || s.h % 8 != 0)) || (S > 1 && (s.s <= 0 || s.s % 8 != 0)))
     return false;
@@ -208,6 +217,10 @@ bool fwd_sm100_covers(int D, int dtype, float scale) {
   // up to the next of them by the bulk copies
   return (dtype == SKB_F16 || dtype == SKB_BF16) && D <= 256 && D % 8 == 0 && scale > 0.f;
 }
+// fp32 through the tensor cores as TF32 (10-bit mantissa operands, fp32 accumulation): only on request
+// (SKB_IMPL_SM100), because the default fp32 path is exact to fp32 rounding and this one is not.
+bool fwd_tf32_covers(int D, int dtype, float scale) { return dtype == SKB_F32 && D <= 128 && D % 4 == 0 && scale > 0.f; }
+
 
 template <typename T, int HD>
 int launch_fwd_sm100(const void* q, const Strides& qs, const void* k, const Strides& ks, const void* v, const Strides& vs,
@@ -231,21 +244,21 @@ int launch_fwd_sm100(const void* q, const Strides& qs, const void* k, const Stri
   return SKB_OK;
 }
 
-// 128 < D <= 256: one 128-row query tile per CTA (decode_tc.cuh); the two-tile kernel has no tensor memory for
-// two 256-column accumulators.
-template <typename T>
-int launch_fwd_tile256(const void* q, const Strides& qs, const void* k, const Strides& ks, const void* v,
+// One 128-row query tile per CTA (decode_tc.cuh): 16-bit 128 < D <= 256 (the two-tile kernel has no tensor memory for
+// two 256-column accumulators) and fp32 D <= 128 (TF32 operands; rows as wide in bytes as 16-bit D = 256).
+template <typename T, int HD>
+int launch_fwd_tile(const void* q, const Strides& qs, const void* k, const Strides& ks, const void* v,
                        const Strides& vs, void* o, const Strides& os, float* lse, int B, int Hq, int Hkv, int Sq, int Sk,
                        int D, int causal, float scale, cudaStream_t st, const Varlen& vl = Varlen{nullptr, nullptr, 0, 0},
                        int total_k = 0) {
-  using C = dtc::Cfg<256>;
+  using C = dtc::Cfg<T, HD>;
   const bool packed = vl.cu_q != nullptr;
   CUtensorMap mq, mk, mv;
   const int dt = DtypeOf<T>::value;
   if (int rc = make_map_4d(&mq, dt, q, D, packed ? vl.total_q : Sq, Hq, packed ? 1 : B, qs)) return rc;
   if (int rc = make_map_4d(&mk, dt, k, D, packed ? total_k : Sk, Hkv, packed ? 1 : B, ks, C::kKvRows)) return rc;
-  if (int rc = make_map_4d(&mv, dt, v, D, packed ? total_k : Sk, Hkv, packed ? 1 : B, vs, C::kKvRows)) return rc;
-  auto kern = dtc::tile_kernel<T, 256, true>;
+  if (int rc = make_map_4d(&mv, dt, v, D, packed ? total_k : Sk, Hkv, packed ? 1 : B, vs, C::kKvRows, dt == SKB_F32)) return rc;
+  auto kern = dtc::tile_kernel<T, HD, true>;
   if (int rc = set_smem(kern, C::kSmemBytes)) return rc;
   const dtc::DecodeArgs dec{PagedKv{nullptr, 0, 0, 0}, nullptr, nullptr, nullptr, 1};
   const dtc::PrefillArgs<T> pre{(T*)o, os, lse, Sq, causal, vl};
@@ -402,7 +415,7 @@ int make_kv_maps(CUtensorMap* mk, CUtensorMap* mv, PagedKv* pg, int dt, const Kv
   const int sub = kv.paged() ? (kv.page_size < tile_rows ? kv.page_size : tile_rows) : tile_rows;
   const int rows = kv.paged() ? kv.page_size : Scap, outer = kv.paged() ? kv.num_pages : B;
   if (int rc = make_map_4d(mk, dt, kv.k, D, rows, Hkv, outer, kv.ks, sub)) return rc;
-  if (int rc = make_map_4d(mv, dt, kv.v, D, rows, Hkv, outer, kv.vs, sub)) return rc;
+  if (int rc = make_map_4d(mv, dt, kv.v, D, rows, Hkv, outer, kv.vs, sub, dt == SKB_F32)) return rc;
   *pg = PagedKv{kv.block_table, kv.max_pages, kv.page_size, sub};
   return SKB_OK;
 }
@@ -424,7 +437,7 @@ template <typename T, int HD>
 int launch_decode_tile(const void* q, const Strides& qs, const KvCache& kv, const int32_t* lens, void* o, const Strides& os,
                        float* lse, int B, int Hq, int Hkv, int Scap, int D, int nsplit, float scale, float* part_o,
                        float2* part_ml, cudaStream_t st) {
-  using C = dtc::Cfg<HD>;
+  using C = dtc::Cfg<T, HD>;
   const int dt = DtypeOf<T>::value;
   CUtensorMap mq, mk, mv;
   PagedKv pg;
@@ -539,6 +552,17 @@ int attn_fwd_impl(const void* q, const Strides& qs, const void* k, const Strides
                      same_strides(ks, contiguous_strides(Hkv, Sk, D), B, Hkv, Sk) &&
                      same_strides(vs, contiguous_strides(Hkv, Sk, D), B, Hkv, Sk) &&
                      same_strides(os, contiguous_strides(Hq, Sq, D), B, Hq, Sq);
+  if (impl == SKB_IMPL_SM100 && fwd_tf32_covers(D, dtype, scale)) {
+    if (!dense) {
+      auto ok4 = [](const void* p, const Strides& s, int nb, int nh, int ns) {
+        return aligned16(p) && (nb == 1 || (s.b > 0 && s.b % 4 == 0)) && (nh == 1 || (s.h > 0 && s.h % 4 == 0)) &&
+               (ns == 1 || (s.s > 0 && s.s % 4 == 0));
+      };
+      if (!ok4(q, qs, B, Hq, Sq) || !ok4(k, ks, B, Hkv, Sk) || !ok4(v, vs, B, Hkv, Sk) || !ok4(o, os, B, Hq, Sq))
+        return SKB_ERR_ALIGN;
+    }
+    return launch_fwd_tile<float, 128>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+  }
   const bool covers = fwd_sm100_covers(D, dtype, scale);
   if ((impl == SKB_IMPL_SM100 || impl == 3 || impl == 4) && !covers) return SKB_ERR_UNSUPPORTED;
   const bool gen2 = impl == 3;   // selector for the alternative forward (Q resident in TMEM, fwd2_sm100.cuh), for A/B timing
@@ -563,8 +587,8 @@ int attn_fwd_impl(const void* q, const Strides& qs, const void* k, const Strides
 #define SKB_FWD(T_, HD_) launch_fwd_sm100<T_, HD_>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st, Varlen{nullptr, nullptr, 0, 0}, 0, persist)
     if (D > 128) {
       if (dtype == SKB_F16)
-        return launch_fwd_tile256<__half>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
-      return launch_fwd_tile256<__nv_bfloat16>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+        return launch_fwd_tile<__half, 256>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
+      return launch_fwd_tile<__nv_bfloat16, 256>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
     }
     if (dtype == SKB_F16) return D <= 64 ? SKB_FWD(__half, 64) : SKB_FWD(__half, 128);
     return D <= 64 ? SKB_FWD(__nv_bfloat16, 64) : SKB_FWD(__nv_bfloat16, 128);
@@ -699,7 +723,7 @@ int skb_attn_fwd_varlen(const void* q, const int64_t* q_strides, const void* k, 
   const Varlen vl{cu_seqlens_q, cu_seqlens_k, total_q, 0};
   cudaStream_t st = (cudaStream_t)stream;
 #define SKB_FWDV(F_) F_(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, max_seqlen_q, max_seqlen_k, D, causal, scale, st, vl, total_k)
-  if (D > 128) return dtype == SKB_F16 ? SKB_FWDV(launch_fwd_tile256<__half>) : SKB_FWDV(launch_fwd_tile256<__nv_bfloat16>);
+  if (D > 128) return dtype == SKB_F16 ? SKB_FWDV((launch_fwd_tile<__half, 256>)) : SKB_FWDV((launch_fwd_tile<__nv_bfloat16, 256>));
   if (dtype == SKB_F16) return D <= 64 ? SKB_FWDV((launch_fwd_sm100<__half, 64>)) : SKB_FWDV((launch_fwd_sm100<__half, 128>));
   return D <= 64 ? SKB_FWDV((launch_fwd_sm100<__nv_bfloat16, 64>)) : SKB_FWDV((launch_fwd_sm100<__nv_bfloat16, 128>));
 #undef SKB_FWDV
@@ -787,8 +811,10 @@ int decode_impl(const void* q, const Strides& qs, const KvCache& kv, const int32
                      same_strides(os, contiguous_strides(Hq, 1, D), B, Hq, 1) &&
                      same_strides(kv.ks, contiguous_strides(Hkv, Scap, D), B, Hkv, Scap) &&
                      same_strides(kv.vs, contiguous_strides(Hkv, Scap, D), B, Hkv, Scap);
+  // fp32 on request (SKB_IMPL_SM100): the one-tile tcgen05 kernel with TF32 operands, dense caches only
+  const bool tf32 = impl == SKB_IMPL_SM100 && dtype == SKB_F32 && D <= 128 && D % 4 == 0 && Hq / Hkv <= 128 && dense;
   const bool group_ok = decode_group_covers(Hq, Hkv, D, dtype);
-  if (impl == SKB_IMPL_SM100 && !group_ok) return SKB_ERR_UNSUPPORTED;
+  if (impl == SKB_IMPL_SM100 && !group_ok && !tf32) return SKB_ERR_UNSUPPORTED;
   const bool use_group = group_ok && impl != SKB_IMPL_GENERAL;
   if (!dense) {
     // strided or paged caches: only the bulk-copy kernels can address them
@@ -805,6 +831,9 @@ int decode_impl(const void* q, const Strides& qs, const KvCache& kv, const int32
   const size_t n = (size_t)B * Hq * num_splits;
   float* part_o = (float*)workspace;
   float2* part_ml = (float2*)((char*)workspace + align_up(n * D * sizeof(float), 256));
+  if (tf32)
+    return launch_decode_tile<float, 128>(q, qs, kv, cache_seqlens, o, os, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o,
+                                          part_ml, st);
   if (use_group) {
 #define SKB_DGRP(T_) decode_group<T_>(q, qs, kv, cache_seqlens, o, os, lse, B, Hq, Hkv, Scap, D, num_splits, scale, part_o, part_ml, st)
     return dtype == SKB_F16 ? SKB_DGRP(__half) : SKB_DGRP(__nv_bfloat16);

@@ -179,6 +179,14 @@ __device__ __forceinline__ uint64_t desc_sw128_mnmajor(uint32_t saddr, uint32_t 
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | (64ull << 32) | (1ull << 46) |
          (2ull << 61);
 }
+// MN-major operand of 32-bit elements (TF32): tcgen05 takes it only in the 128-byte swizzle with 32-byte atoms
+// (layout type 1; tensor maps: SWIZZLE_128B_ATOM_32B).  Rows are still 128 bytes (32 elements of the M/N index);
+// the swizzle pattern repeats every 4 K rows, so the stride between K groups (SBO) is 512 bytes; the next 32 M/N
+// elements are `lbo_bytes` on.
+__device__ __forceinline__ uint64_t desc_sw128_atom32_mnmajor(uint32_t saddr, uint32_t lbo_bytes) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | (32ull << 32) | (1ull << 46) |
+         (1ull << 61);
+}
 // Instruction descriptor for kind::f16 with fp32 accumulation.
 // fmt: 0 = fp16, 1 = bf16.  a_mn / b_mn: 1 if that operand is MN-major.
 __host__ __device__ constexpr uint32_t idesc_f16(int fmt, int M, int N, int a_mn, int b_mn) {
@@ -201,6 +209,24 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same two forms for fp32 operands used as TF32 (kind::tf32: 8 elements of K per instruction; operand
+// format 2 in the instruction descriptor; A from TMEM is one 32-bit value per column).
+__device__ __forceinline__ void mma_ss_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }

@@ -56,7 +56,7 @@ def test_argument_validation_happens_on_host(lib):
     assert fwd(Sq=0) == _lib.SKB_ERR_SHAPE
     assert fwd(dt=7) == _lib.SKB_ERR_DTYPE
     assert fwd(q=ctypes.c_void_p((1 << 20) + 4)) == _lib.SKB_ERR_ALIGN
-    assert fwd(impl=_lib.IMPL_SM100) == _lib.SKB_ERR_UNSUPPORTED     # fp32 has no tensor-core path
+    assert fwd(impl=_lib.IMPL_SM100, D=132) == _lib.SKB_ERR_UNSUPPORTED   # fp32 tensor-core (TF32) path stops at D = 128
     # backward without workspace, decode with too many splits
     rc = lib.skb_attn_bwd(p, p, p, p, p, p, p, p, p, 1, 4, 2, 8, 8, 64, 0, 0, 0.125, 0, None, 0, None)
     assert rc == _lib.SKB_ERR_WORKSPACE

@@ -212,6 +212,52 @@ def test_tensor_core_backward_vs_oracle(skb, name):
     _check_status()
 
 
+# fp32 through the tensor cores as TF32 (opt-in: impl="sm100"); bar 2e-3 as for every fp32 result
+TF32_CASES = {
+    "config1_shape": dict(B=2, Hq=8, Hkv=8, Sq=512, Sk=512, D=64, causal=True, seed=0),
+    "gqa_s300x420_d128_causal": dict(B=1, Hq=4, Hkv=2, Sq=300, Sk=420, D=128, causal=True, seed=91),
+    "mqa_s200_d96_full": dict(B=2, Hq=4, Hkv=1, Sq=200, Sk=200, D=96, causal=False, seed=92),
+    "mha_s129x70_d32_causal": dict(B=1, Hq=2, Hkv=2, Sq=129, Sk=70, D=32, causal=True, seed=93),
+}
+
+
+@pytest.mark.parametrize("name", sorted(TF32_CASES))
+def test_fp32_forward_on_tensor_cores_tf32(skb, name):
+    from oracle import attention_oracle as orc
+    from stackkernels_b200.launchers import flash_attn_fwd
+    c = TF32_CASES[name]
+    torch.manual_seed(c["seed"])
+    q = torch.randn(c["B"], c["Hq"], c["Sq"], c["D"])
+    k = torch.randn(c["B"], c["Hkv"], c["Sk"], c["D"])
+    v = torch.randn(c["B"], c["Hkv"], c["Sk"], c["D"])
+    eo, el = orc.attention_forward(q, k, v, causal=c["causal"])
+    o, lse = flash_attn_fwd(q.cuda(), k.cuda(), v.cuda(), is_causal=c["causal"], impl="sm100")
+    torch.cuda.synchronize()
+    assert_parity(o, eo, "fp32", f"{name} O (TF32)")
+    assert_parity(lse, el, "fp32", f"{name} LSE (TF32)")
+    # the default fp32 path stays exact to fp32 rounding
+    o_exact, _ = flash_attn_fwd(q.cuda(), k.cuda(), v.cuda(), is_causal=c["causal"])
+    assert (o_exact.cpu() - eo).abs().max().item() <= 2e-5
+    _check_status()
+
+
+def test_fp32_decode_on_tensor_cores_tf32(skb):
+    from oracle import attention_oracle as orc
+    from stackkernels_b200.launchers import flash_decode as core
+    torch.manual_seed(94)
+    q = torch.randn(3, 8, 1, 128)
+    k, v = torch.randn(3, 2, 1500, 128), torch.randn(3, 2, 1500, 128)
+    lens = torch.tensor([1500, 0, 333], dtype=torch.int32)
+    eo, el = orc.decode_forward(q, k, v, cache_seqlens=lens)
+    for splits in (0, 1, 5):
+        o, lse = core(q.cuda(), k.cuda(), v.cuda(), cache_seqlens=lens.cuda(), return_lse=True, num_splits=splits,
+                      impl="sm100")
+        torch.cuda.synchronize()
+        assert_parity(o, eo, "fp32", f"fp32 decode TF32 [splits={splits}] O")
+        assert_parity(lse, el, "fp32", f"fp32 decode TF32 [splits={splits}] LSE")
+    _check_status()
+
+
 def test_reference_test_matrix_public_api(skb):
     """The reference's own forward test (tests/ops/test_flash_attn.py:10-36): rtol=atol=1e-3, fp32."""
     from oracle import attention_oracle as orc
