@@ -48,7 +48,9 @@ typedef enum skb_status {
 enum {
   SKB_IMPL_AUTO = 0,     /* tcgen05/TMA kernels where the shape qualifies, else the general kernels */
   SKB_IMPL_GENERAL = 1,  /* fp32 CUDA-core kernels: any dtype, any D <= 256 */
-  SKB_IMPL_SM100 = 2     /* tensor-core kernels only; SKB_ERR_UNSUPPORTED if the shape does not qualify */
+  SKB_IMPL_SM100 = 2     /* tensor-core kernels only; SKB_ERR_UNSUPPORTED if the shape does not qualify.  For fp32
+                          * forward and decode (D <= 128) this selects TF32 operands with fp32 accumulation:
+                          * errors of a few 1e-4 instead of fp32 rounding, which is why it is never the default */
 };
 
 /* Prefill forward.  Replaces flash_attn_fwd(q, k, v, is_causal, sm_scale) -> (out, lse)
