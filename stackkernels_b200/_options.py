@@ -20,6 +20,9 @@ class Options:
             backend = os.environ.get("STACKKERNELS_BACKEND", "auto")
         self._backend = "auto"
         self.backend = backend
+        # fp32 tensors through the tensor cores as TF32 (forward and decode): off unless asked for, because the
+        # default fp32 kernels are exact to fp32 rounding and TF32 is not (errors of a few 1e-4)
+        self.allow_tf32 = os.environ.get("STACKKERNELS_ALLOW_TF32", "0").strip().lower() in ("1", "true", "yes")
 
     @property
     def backend(self) -> str:
@@ -47,7 +50,19 @@ def set_backend(backend: str) -> None:
     _GLOBAL_OPTIONS.backend = backend
 
 
-def options(backend: str | None = None) -> Options:
+def options(backend: str | None = None, allow_tf32: bool | None = None) -> Options:
     if backend is not None:
         set_backend(backend)
+    if allow_tf32 is not None:
+        _GLOBAL_OPTIONS.allow_tf32 = bool(allow_tf32)
     return _GLOBAL_OPTIONS
+
+
+def fp32_impl(q, k) -> str:
+    """Implementation selector for a forward / decode call: ``"sm100"`` (TF32 tensor cores) for fp32 tensors the
+    TF32 kernels cover when ``allow_tf32`` is set, else ``"auto"``."""
+    import torch
+    if (_GLOBAL_OPTIONS.allow_tf32 and q.dtype == torch.float32 and q.shape[-1] <= 128 and q.shape[-1] % 4 == 0
+            and k.shape[2] >= 128 and q.is_contiguous() and k.is_contiguous()):
+        return "sm100"
+    return "auto"

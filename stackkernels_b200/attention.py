@@ -16,7 +16,7 @@ from typing import Any
 import torch
 import torch.nn as nn
 
-from ._options import get_backend
+from ._options import fp32_impl, get_backend
 from .launchers import flash_attn_bwd, flash_attn_fwd
 from .launchers import flash_decode as core_flash_decode
 
@@ -62,7 +62,7 @@ class FlashAttentionFunction(torch.autograd.Function):
         ctx.sm_scale = sm_scale
         # Strided views go to the launcher as they are: the tensor-core kernels read them in place, and the
         # launcher copies (as the reference does here, torch/attention.py:38-40) only when they cannot.
-        out, lse = flash_attn_fwd(q, k, v, is_causal=ctx.is_causal, sm_scale=sm_scale)
+        out, lse = flash_attn_fwd(q, k, v, is_causal=ctx.is_causal, sm_scale=sm_scale, impl=fp32_impl(q, k))
         ctx.save_for_backward(q, k, v, out, lse)
         return out
 
@@ -86,7 +86,7 @@ def flash_attention(q, k, v, is_causal: bool = False, sm_scale: float | None = N
     sm_scale = _merge_alias(sm_scale, softmax_scale, None, ("sm_scale", "softmax_scale"))
     if return_lse:
         _require_native(q, "flash_attention")
-        return flash_attn_fwd(q, k, v, is_causal=is_causal, sm_scale=sm_scale)
+        return flash_attn_fwd(q, k, v, is_causal=is_causal, sm_scale=sm_scale, impl=fp32_impl(q, k))
     return FlashAttentionFunction.apply(q, k, v, is_causal, sm_scale)
 
 
@@ -116,7 +116,8 @@ def flash_decode(q, k=None, v=None, sm_scale: float | None = None, *, cache_seql
         else:
             cache_seqlens = torch.full((q.shape[0],), int(start_pos) + 1, dtype=torch.int32, device=q.device)
     _require_native(q, "flash_decode")
-    return core_flash_decode(q, k, v, sm_scale=sm_scale, cache_seqlens=cache_seqlens, return_lse=return_lse)
+    return core_flash_decode(q, k, v, sm_scale=sm_scale, cache_seqlens=cache_seqlens, return_lse=return_lse,
+                             impl=fp32_impl(q, k) if v.is_contiguous() else "auto")
 
 
 class FlashAttention(nn.Module):
@@ -138,7 +139,7 @@ try:
     @torch.library.custom_op("stackkernels_b200::flash_attn_op", mutates_args=())
     def _flash_attn_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool,
                        sm_scale: float | None) -> torch.Tensor:
-        return flash_attn_fwd(q, k, v, is_causal=is_causal, sm_scale=sm_scale)[0]
+        return flash_attn_fwd(q, k, v, is_causal=is_causal, sm_scale=sm_scale, impl=fp32_impl(q, k))[0]
 
     @_flash_attn_op.register_fake
     def _flash_attn_op_fake(q, k, v, is_causal, sm_scale):

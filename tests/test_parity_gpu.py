@@ -258,6 +258,23 @@ def test_fp32_decode_on_tensor_cores_tf32(skb):
     _check_status()
 
 
+def test_allow_tf32_option_routes_the_public_api(skb):
+    """options(allow_tf32=True) sends fp32 flash_attention / flash_decode to the TF32 kernels; off by default."""
+    from stackkernels_b200.launchers import flash_attn_fwd
+    torch.manual_seed(95)
+    q, k, v = (torch.randn(1, 4, 256, 64).cuda() for _ in range(3))
+    exact = skb.flash_attention(q, k, v, is_causal=True)
+    assert torch.equal(exact, flash_attn_fwd(q, k, v, is_causal=True)[0])
+    skb.options(allow_tf32=True)
+    try:
+        fast = skb.flash_attention(q, k, v, is_causal=True)
+        assert torch.equal(fast, flash_attn_fwd(q, k, v, is_causal=True, impl="sm100")[0])
+        assert not torch.equal(fast, exact) and (fast - exact).abs().max().item() <= 2e-3
+    finally:
+        skb.options(allow_tf32=False)
+    _check_status()
+
+
 def test_reference_test_matrix_public_api(skb):
     """The reference's own forward test (tests/ops/test_flash_attn.py:10-36): rtol=atol=1e-3, fp32."""
     from oracle import attention_oracle as orc
