@@ -313,7 +313,7 @@ def run_native(args):
         line["cpu_baseline"] = cpu_baseline(name, limit_s=args.cpu_seconds)
     if world == 1 and not args.no_extras:
         extras = {}
-        for en, st in (("prefill_fwd_s8192", 5), ("fwdbwd_c3", 2), ("decode_c4", 10), ("decode_c5", 10), ("rope_c3", 10)):
+        for en, st in (("prefill_fwd_s8192", 5), ("fwdbwd_c3", 3), ("decode_c4", 10), ("decode_c5", 10), ("rope_c3", 10)):
             if en == name:
                 continue
             torch.cuda.empty_cache()
