@@ -337,6 +337,8 @@ def cpu_baseline(name, limit_s=15.0):
     kind, p = WORKLOADS[name]
     torch.manual_seed(p["seed"])
     dt = DT[p["dtype"]]
+    # all host cores, whatever the launcher put into OMP_NUM_THREADS (torchrun sets it to 1 per process)
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)))
     threads = torch.get_num_threads()
     done_units, t_used, n = 0.0, 0.0, 0
     if kind in ("fwd", "bwd"):
