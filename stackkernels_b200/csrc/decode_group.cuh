@@ -90,6 +90,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int G = Hq / Hkv;
+  // the combine kernel behind this one is launched as a programmatic dependent; letting it be scheduled right away
+  // costs nothing (its CTAs block on the grid dependency) and hides its launch latency
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int len = seqlens ? min(max(seqlens[b], 0), Scap) : Scap;
   const int chunk = cdiv(cdiv(len, nsplit), kTileN) * kTileN;
   const int start = split * chunk;

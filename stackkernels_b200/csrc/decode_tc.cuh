@@ -101,6 +101,9 @@ tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   const int lane = threadIdx.x & 31;
   const int G = Hq / Hkv;
   const int b = blockIdx.z;
+  // decode: the combine kernel behind this one is launched as a programmatic dependent; letting it be scheduled
+  // right away costs nothing (its CTAs block on the grid dependency) and hides its launch latency
+  if (!PREFILL) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // decode: blockIdx = (split, kv head, batch); prefill: (query tile, q head, batch), heaviest tiles first
   const int split = PREFILL ? 0 : blockIdx.x;
   const int hq = PREFILL ? blockIdx.y : 0;

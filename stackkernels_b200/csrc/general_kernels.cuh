@@ -523,6 +523,10 @@ decode_combine_kernel(const float* __restrict__ part_o, const float2* __restrict
   __shared__ float s_ML[2];
   const size_t bh = blockIdx.x;
   const float2* ml = part_ml + bh * nsplit;
+  // Launched with programmatic stream serialization: this grid may start while the split kernel is still
+  // draining, so that its launch latency is hidden; nothing the split kernel wrote may be read before this wait
+  // (it returns once the whole previous grid has finished and its writes are visible).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x < 32) {
     float M = -INFINITY;
     for (int s = threadIdx.x; s < nsplit; s += 32) M = fmaxf(M, ml[s].x);

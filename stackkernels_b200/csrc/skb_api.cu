@@ -116,6 +116,25 @@ int launch_decode_general(const void* q, const void* kc, const void* vc, const i
   return SKB_OK;
 }
 
+// The LSE-combine kernel, launched so that it may begin while the split kernel in front of it is still draining
+// (programmatic dependent launch); the kernel itself waits for that grid before it reads the partials.
+template <typename T>
+int launch_combine(const float* part_o, const float2* part_ml, void* o, const Strides& os, float* lse, int B, int Hq,
+                   int D, int nsplit, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(B * Hq));
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  SKB_CUDA(cudaLaunchKernelEx(&cfg, general::decode_combine_kernel<T>, part_o, part_ml, (T*)o, os, lse, Hq, D, nsplit));
+  return SKB_OK;
+}
+
 template <typename T>
 int decode_general(const void* q, const void* kc, const void* vc, const int32_t* lens, void* o, float* lse, int B, int Hq,
                    int Hkv, int Scap, int D, int nsplit, float scale, float* part_o, float2* part_ml, cudaStream_t st) {
@@ -127,9 +146,7 @@ int decode_general(const void* q, const void* kc, const void* vc, const int32_t*
   else if (ch <= 32) rc = launch_decode_general<T, 32, 1>(q, kc, vc, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st);
   else rc = launch_decode_general<T, 32, 2>(q, kc, vc, lens, part_o, part_ml, B, Hq, Hkv, Scap, D, nsplit, scale, st);
   if (rc) return rc;
-  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, contiguous_strides(Hq, 1, D), lse, Hq, D, nsplit);
-  SKB_CUDA(cudaGetLastError());
-  return SKB_OK;
+  return launch_combine<T>(part_o, part_ml, o, contiguous_strides(Hq, 1, D), lse, B, Hq, D, nsplit, st);
 }
 
 // ------------------------------------------------------------------------------------ tensor-core forward
@@ -449,9 +466,7 @@ int launch_decode_tile(const void* q, const Strides& qs, const KvCache& kv, cons
   const dtc::PrefillArgs<T> pre{nullptr, Strides{0, 0, 0}, nullptr, 1, 0, Varlen{nullptr, nullptr, 0, 0}};
   kern<<<dim3(nsplit, Hkv, B), dtc::kThreads, C::kSmemBytes, st>>>(mq, mk, mv, dec, pre, Hq, Hkv, Scap, D, scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
-  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, os, lse, Hq, D, nsplit);
-  SKB_CUDA(cudaGetLastError());
-  return SKB_OK;
+  return launch_combine<T>(part_o, part_ml, o, os, lse, B, Hq, D, nsplit, st);
 }
 
 template <typename T>
@@ -474,9 +489,7 @@ int decode_group(const void* q, const Strides& qs, const KvCache& kv, const int3
   else rc = G <= 16 ? SKB_DG(128, 1) : (G <= 32 ? SKB_DG(128, 2) : SKB_DG(128, 4));
 #undef SKB_DG
   if (rc) return rc;
-  general::decode_combine_kernel<T><<<(unsigned)(B * Hq), 128, 0, st>>>(part_o, part_ml, (T*)o, os, lse, Hq, D, nsplit);
-  SKB_CUDA(cudaGetLastError());
-  return SKB_OK;
+  return launch_combine<T>(part_o, part_ml, o, os, lse, B, Hq, D, nsplit, st);
 }
 
 // ------------------------------------------------------------------------------------ built-in decode scratch
