@@ -9,7 +9,6 @@
 #include "decode_group.cuh"
 #include "decode_tc.cuh"
 #include "bwd_sm100.cuh"
-#include "fwd2_sm100.cuh"
 #include "aux_kernels.cuh"
 #include "general_kernels.cuh"
 #include "skb200.h"
@@ -281,22 +280,6 @@ int launch_fwd_tile(const void* q, const Strides& qs, const void* k, const Strid
   const dtc::PrefillArgs<T> pre{(T*)o, os, lse, Sq, causal, vl};
   kern<<<dim3(cdiv(Sq, 128), Hq, B), dtc::kThreads, C::kSmemBytes, st>>>(mq, mk, mv, dec, pre, Hq, Hkv, Sk, D,
                                                                         scale * kLog2e);
-  SKB_CUDA(cudaGetLastError());
-  return SKB_OK;
-}
-
-template <typename T>
-int launch_fwd2_sm100(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Hq, int Hkv, int Sq,
-                      int Sk, int causal, float scale, cudaStream_t st) {
-  CUtensorMap mk, mv;
-  const int dt = DtypeOf<T>::value;
-  if (int rc = make_map_4d(&mk, dt, k, 128, Sk, Hkv, B, contiguous_strides(Hkv, Sk, 128))) return rc;
-  if (int rc = make_map_4d(&mv, dt, v, 128, Sk, Hkv, B, contiguous_strides(Hkv, Sk, 128))) return rc;
-  auto kern = sm100::fwd2_kernel<T>;
-  if (int rc = set_smem(kern, sm100::kF2SmemBytes)) return rc;
-  dim3 grid(cdiv(Sq, 128), Hq, B);
-  kern<<<grid, sm100::kF2Threads, sm100::kF2SmemBytes, st>>>((const T*)q, mk, mv, (T*)o, lse, Hq, Hkv, Sq, Sk, causal,
-                                                            scale * kLog2e);
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }
@@ -577,24 +560,19 @@ int attn_fwd_impl(const void* q, const Strides& qs, const void* k, const Strides
     return launch_fwd_tile<float, 128>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st);
   }
   const bool covers = fwd_sm100_covers(D, dtype, scale);
-  if ((impl == SKB_IMPL_SM100 || impl == 3 || impl == 4) && !covers) return SKB_ERR_UNSUPPORTED;
-  const bool gen2 = impl == 3;   // selector for the alternative forward (Q resident in TMEM, fwd2_sm100.cuh), for A/B timing
+  if ((impl == SKB_IMPL_SM100 || impl == 4) && !covers) return SKB_ERR_UNSUPPORTED;
   // CTAs keep taking work items (cluster launch control) unless an item is so long that its start-up and
   // epilogue do not matter (measured on B200: +17 % at S=1024, +3 % at 4096, +1.5 % at 8192, -1 % at 16384,
   // -2 % at 32768, where the kernel runs into the power cap either way).  Selector 4 forces one item per CTA.
   const int persist = (impl == 4 || Sk > 12288) ? 0 : 1;
-  if (gen2 || impl == 4) impl = SKB_IMPL_SM100;
+  if (impl == 4) impl = SKB_IMPL_SM100;
   const bool use_tc = impl == SKB_IMPL_SM100 || (impl == SKB_IMPL_AUTO && covers && Sq >= 128 && Sk >= 128);
   if (!dense) {
     // strided tensors: only the bulk-copy kernels can address them
-    if (!use_tc || gen2) return SKB_ERR_UNSUPPORTED;
+    if (!use_tc) return SKB_ERR_UNSUPPORTED;
     if (!strides_ok(q, qs, B, Hq, Sq) || !strides_ok(k, ks, B, Hkv, Sk) || !strides_ok(v, vs, B, Hkv, Sk) ||
         !strides_ok(o, os, B, Hq, Sq))
       return SKB_ERR_ALIGN;
-  }
-  if (use_tc && D == 128 && gen2) {
-    if (dtype == SKB_F16) return launch_fwd2_sm100<__half>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
-    return launch_fwd2_sm100<__nv_bfloat16>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, causal, scale, st);
   }
   if (use_tc) {
 #define SKB_FWD(T_, HD_) launch_fwd_sm100<T_, HD_>(q, qs, k, ks, v, vs, o, os, lse, B, Hq, Hkv, Sq, Sk, D, causal, scale, st, Varlen{nullptr, nullptr, 0, 0}, 0, persist)
