@@ -13,59 +13,74 @@ namespace aux {
 // Backward (src/stackkernels/torch/embedding.py:46-64):        dx  = dy*cos - rotate_half(dy)*sin.
 // With out_bhsd the result is written as (B, H, S, D), the layout the attention kernels take, which
 // saves the transpose + contiguous copy callers otherwise make.
-// One CTA per (batch, position): a thread owns VE consecutive columns of the first half (and their partners in
-// the second half), loads its cos/sin values once with vector loads and applies them to every head it loops over.
+// Grid (batch * positions, rounds): a CTA stages its position's cos/sin row in shared memory as fp32 (2*D floats of
+// dynamic shared memory) and rotates 2 * (256 / vectors per half row) heads of that position; a thread owns VE
+// consecutive columns of the first half (and their partners in the second half) of two heads.  The kernel is pure
+// streaming, so what matters is bytes in flight: a thread issues the loads of both heads (64 bytes) before the table
+// is staged, and keeping the table out of registers leaves room for more resident CTAs per SM.
 // ------------------------------------------------------------------------------------------------
-template <typename TT, int VE>
-__device__ __forceinline__ void load_table(const TT* __restrict__ p, float* out) {
-  if constexpr (sizeof(TT) == 4) {
-#pragma unroll
-    for (int i = 0; i < VE; i += 4) {
-      const float4 v = __ldg(reinterpret_cast<const float4*>(p + i));
-      out[i] = v.x; out[i + 1] = v.y; out[i + 2] = v.z; out[i + 3] = v.w;
-    }
-  } else {
-    load_vec16<TT>(p, out);     // VE == 8 sixteen-bit values = one 16-byte vector
-  }
-}
-
 template <typename T, typename TT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 rope_kernel(const T* __restrict__ x, const TT* __restrict__ cos_t, const TT* __restrict__ sin_t, T* __restrict__ out,
             int S, int H, int D, int start_pos, int backward, int out_bhsd) {
   constexpr int VE = Vec16<T>::N;
+  extern __shared__ float s_table[];                 // cos row [0, D), sin row [D, 2D)
   const int half = D / 2;
-  const int vph = half / VE;                         // vectors per half row (<= 256 / 1)
+  const int vph = half / VE;                         // vectors per half row (<= 256)
   const int tid = threadIdx.x;
   const int hstep = 256 / vph;                       // heads covered per pass
   const int c = (tid % vph) * VE;
+  const int h0 = tid / vph;
+  const bool active = h0 < hstep;                    // threads beyond a whole number of heads per pass only stage
   const size_t bs = blockIdx.x;                      // b*S + s
   const int s = (int)(bs % S);
   const size_t b = bs / S;
-  if (tid / vph >= hstep) return;                    // threads beyond a whole number of heads per pass
-  float c1[VE], c2[VE], s1[VE], s2[VE];
-  const size_t trow = (size_t)(start_pos + s) * D;
-  load_table<TT, VE>(cos_t + trow + c, c1);
-  load_table<TT, VE>(cos_t + trow + half + c, c2);
-  load_table<TT, VE>(sin_t + trow + c, s1);
-  load_table<TT, VE>(sin_t + trow + half + c, s2);
-  const float sg = backward ? -1.f : 1.f;            // forward: +rot*sin ; backward: -rot*sin
-  for (int h = tid / vph; h < H; h += hstep) {
-    const T* xr = x + (bs * H + h) * D;
-    float x1[VE], x2[VE];
-    load_vec16<T>(xr + c, x1);
-    load_vec16<T>(xr + half + c, x2);
-    T o1[VE], o2[VE];
+
+  uint4 r1[2], r2[2];                                // raw vectors of two heads: first-half and second-half columns
+  auto load_round = [&](int hb) {
 #pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      // rot[:half] = -x2, rot[half:] = x1
-      o1[e] = from_f<T>(x1[e] * c1[e] + sg * (-x2[e]) * s1[e]);
-      o2[e] = from_f<T>(x2[e] * c2[e] + sg * x1[e] * s2[e]);
+    for (int u = 0; u < 2; ++u) {
+      const int h = hb + u * hstep;
+      if (h < H) {
+        const T* xr = x + (bs * H + h) * D;
+        r1[u] = __ldg(reinterpret_cast<const uint4*>(xr + c));
+        r2[u] = __ldg(reinterpret_cast<const uint4*>(xr + half + c));
+      }
     }
-    const size_t orow = out_bhsd ? ((b * H + h) * S + s) : (bs * H + h);
-    *reinterpret_cast<uint4*>(out + orow * D + c) = *reinterpret_cast<const uint4*>(o1);
-    *reinterpret_cast<uint4*>(out + orow * D + half + c) = *reinterpret_cast<const uint4*>(o2);
+  };
+  const float sg = backward ? -1.f : 1.f;            // forward: +rot*sin ; backward: -rot*sin
+  auto rotate_round = [&](int hb) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int h = hb + u * hstep;
+      if (h >= H) break;
+      float x1[VE], x2[VE];
+      unpack_vec16<T>(r1[u], x1);
+      unpack_vec16<T>(r2[u], x2);
+      T o1[VE], o2[VE];
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float c1 = s_table[c + e], c2 = s_table[half + c + e];
+        const float s1 = s_table[D + c + e], s2 = s_table[D + half + c + e];
+        // rot[:half] = -x2, rot[half:] = x1
+        o1[e] = from_f<T>(x1[e] * c1 + sg * (-x2[e]) * s1);
+        o2[e] = from_f<T>(x2[e] * c2 + sg * x1[e] * s2);
+      }
+      const size_t orow = out_bhsd ? ((b * H + h) * S + s) : (bs * H + h);
+      *reinterpret_cast<uint4*>(out + orow * D + c) = *reinterpret_cast<const uint4*>(o1);
+      *reinterpret_cast<uint4*>(out + orow * D + half + c) = *reinterpret_cast<const uint4*>(o2);
+    }
+  };
+
+  const int hb = h0 + (int)blockIdx.y * 2 * hstep;   // grid.y = rounds of 2*hstep heads
+  if (active) load_round(hb);
+  const size_t trow = (size_t)(start_pos + s) * D;
+  for (int i = tid; i < D; i += 256) {
+    s_table[i] = to_f(cos_t[trow + i]);
+    s_table[D + i] = to_f(sin_t[trow + i]);
   }
+  __syncthreads();
+  if (active) rotate_round(hb);
 }
 
 // ------------------------------------------------------------------------------------------------

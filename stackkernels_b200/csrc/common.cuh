@@ -64,10 +64,9 @@ inline int varlen_total_pad(int total_q, int B) { return ((total_q + 127) & ~127
 
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
 
-// Load 16 bytes (Vec16<T>::N elements) from global memory and widen to fp32.
+// Widen the Vec16<T>::N elements of a 16-byte vector to fp32.
 template <typename T>
-__device__ __forceinline__ void load_vec16(const T* __restrict__ p, float* out) {
-  uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+__device__ __forceinline__ void unpack_vec16(const uint4& raw, float* out) {
   if constexpr (sizeof(T) == 4) {
     out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y);
     out[2] = __uint_as_float(raw.z); out[3] = __uint_as_float(raw.w);
@@ -76,6 +75,13 @@ __device__ __forceinline__ void load_vec16(const T* __restrict__ p, float* out) 
 #pragma unroll
     for (int i = 0; i < 8; ++i) out[i] = to_f(e[i]);
   }
+}
+
+// Load 16 bytes (Vec16<T>::N elements) from global memory and widen to fp32.
+template <typename T>
+__device__ __forceinline__ void load_vec16(const T* __restrict__ p, float* out) {
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  unpack_vec16<T>(raw, out);
 }
 
 }  // namespace skb

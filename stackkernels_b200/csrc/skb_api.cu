@@ -917,9 +917,10 @@ int skb_rope(const void* x, const void* cos_table, const void* sin_table, void* 
   cudaStream_t st = (cudaStream_t)stream;
   if (D / 2 / ve > 256 || (size_t)B * S > 0x7fffffffull) return SKB_ERR_TOO_LARGE;
   if (!aligned16(cos_table) || !aligned16(sin_table)) return SKB_ERR_ALIGN;
-  const unsigned blocks = (unsigned)((size_t)B * S);
+  const int heads_per_cta = 2 * (256 / (D / 2 / ve));     // two passes of the heads one pass of 256 threads covers
+  const dim3 blocks((unsigned)((size_t)B * S), (unsigned)cdiv(H, heads_per_cta));
 #define SKB_ROPE(T_, TT_)                                                                                         \
-  aux::rope_kernel<T_, TT_><<<blocks, 256, 0, st>>>((const T_*)x, (const TT_*)cos_table, (const TT_*)sin_table,   \
+  aux::rope_kernel<T_, TT_><<<blocks, 256, 2 * (size_t)D * sizeof(float), st>>>((const T_*)x, (const TT_*)cos_table, (const TT_*)sin_table,   \
                                                     (T_*)out, S, H, D, start_pos, backward, out_bhsd)
   if (dtype == SKB_F32) SKB_ROPE(float, float);
   else if (dtype == SKB_F16) { if (table_dtype == SKB_F32) SKB_ROPE(__half, float); else SKB_ROPE(__half, __half); }
