@@ -917,15 +917,34 @@ int skb_rope(const void* x, const void* cos_table, const void* sin_table, void* 
   cudaStream_t st = (cudaStream_t)stream;
   if (D / 2 / ve > 256 || (size_t)B * S > 0x7fffffffull) return SKB_ERR_TOO_LARGE;
   if (!aligned16(cos_table) || !aligned16(sin_table)) return SKB_ERR_ALIGN;
-  const int heads_per_cta = 2 * (256 / (D / 2 / ve));     // two passes of the heads one pass of 256 threads covers
-  const dim3 blocks((unsigned)((size_t)B * S), (unsigned)cdiv(H, heads_per_cta));
+  const long long n_rows = (long long)B * S * H;
+  const int rows_per_cta = aux::rope_rows_per_cta(D, ve);
+  const long long n_blocks = (n_rows + rows_per_cta - 1) / rows_per_cta;
+  if (n_blocks > 0x7fffffffll) return SKB_ERR_TOO_LARGE;
+  const size_t smem = (size_t)aux::rope_positions_per_cta(D, ve, H) * 2 * D * sizeof(float);
+  // a CTA's rows = whole positions (pos_per_cta), or a position = whole CTAs (cta_per_pos), or neither (both 0)
+  const int cta_per_pos = H % rows_per_cta == 0 ? H / rows_per_cta : 0;
+  const int pos_per_cta = (cta_per_pos == 0 && rows_per_cta % H == 0) ? rows_per_cta / H : 0;
+#define SKB_ROPE_LAUNCH(T_, TT_, MODE_)                                                                            \
+  do {                                                                                                            \
+    auto kern = aux::rope_kernel<T_, TT_, MODE_>;                                                                 \
+    if (smem > 48 * 1024) { if (int rc = set_smem(kern, smem)) return rc; }                                       \
+    kern<<<(unsigned)n_blocks, 256, smem, st>>>((const T_*)x, (const TT_*)cos_table, (const TT_*)sin_table,       \
+                                                (T_*)out, S, H, D, start_pos, backward, out_bhsd, n_rows,         \
+                                                pos_per_cta, cta_per_pos);                                        \
+  } while (0)
 #define SKB_ROPE(T_, TT_)                                                                                         \
-  aux::rope_kernel<T_, TT_><<<blocks, 256, 2 * (size_t)D * sizeof(float), st>>>((const T_*)x, (const TT_*)cos_table, (const TT_*)sin_table,   \
-                                                    (T_*)out, S, H, D, start_pos, backward, out_bhsd)
+  do {                                                                                                            \
+    if (cta_per_pos == 1) SKB_ROPE_LAUNCH(T_, TT_, 3);                                                           \
+    else if (cta_per_pos > 0) SKB_ROPE_LAUNCH(T_, TT_, 0);                                                       \
+    else if (pos_per_cta > 0) SKB_ROPE_LAUNCH(T_, TT_, 1);                                                        \
+    else SKB_ROPE_LAUNCH(T_, TT_, 2);                                                                             \
+  } while (0)
   if (dtype == SKB_F32) SKB_ROPE(float, float);
   else if (dtype == SKB_F16) { if (table_dtype == SKB_F32) SKB_ROPE(__half, float); else SKB_ROPE(__half, __half); }
   else { if (table_dtype == SKB_F32) SKB_ROPE(__nv_bfloat16, float); else SKB_ROPE(__nv_bfloat16, __nv_bfloat16); }
 #undef SKB_ROPE
+#undef SKB_ROPE_LAUNCH
   SKB_CUDA(cudaGetLastError());
   return SKB_OK;
 }

@@ -61,6 +61,29 @@ def test_rope_kernel_vs_reference(name):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("B,S,H,D,dtype", [(3, 50, 5, 128, torch.bfloat16), (2, 31, 1, 64, torch.float16),
+                                           (2, 9, 100, 32, torch.float32), (1, 7, 3, 512, torch.bfloat16),
+                                           (2, 300, 8, 128, torch.bfloat16)])
+def test_rope_rows_across_positions(B, S, H, D, dtype):
+    """A CTA rotates a fixed number of consecutive (position, head) rows, so with these head counts its rows start
+    and end in the middle of a position and cross batch boundaries; forward, backward and the fused layout change
+    must agree with the oracle (the kernel fuses multiply-adds: a few fp32 roundings of difference, i.e. at most one
+    ulp of a 16-bit result, are allowed)."""
+    _gpu()
+    from stackkernels_b200.embedding import rope_launch
+    torch.manual_seed(5)
+    x = torch.randn(B, S, H, D).to(dtype)
+    cos, sin = ro.precompute_freqs(D, S + 11)
+    tol = dict(atol=2e-6, rtol=2e-6) if dtype == torch.float32 else dict(atol=1e-5, rtol=2.0 ** -7)
+    y = rope_launch(x.cuda(), cos.cuda(), sin.cuda(), 11)
+    torch.testing.assert_close(y.cpu().float(), ro.rope_forward(x, cos, sin, 11).float(), **tol)
+    dx = rope_launch(x.cuda(), cos.cuda(), sin.cuda(), 11, backward=True)
+    torch.testing.assert_close(dx.cpu().float(), ro.rope_backward(x, cos, sin, 11).float(), **tol)
+    yt = rope_launch(x.cuda(), cos.cuda(), sin.cuda(), 11, out_bhsd=True)
+    assert torch.equal(yt, y.transpose(1, 2).contiguous())
+
+
+@pytest.mark.gpu
 def test_rope_gqa_and_module():
     skb = _gpu()
     torch.manual_seed(0)
