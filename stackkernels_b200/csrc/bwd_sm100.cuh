@@ -89,8 +89,8 @@ bwd_prep_kernel(const T* __restrict__ dout, const Strides do_str, const T* __res
                 int Sq_pad, int D) {
   constexpr int VE = Vec16<T>::N;
   // grid = (Sq_pad / 64, Hq, B).  A row is D / VE 16-byte vectors; a warp takes as many whole rows as fit its 32
-  // lanes (2 at D = 128 in 16 bits) and every thread issues the loads of two rows' vectors before it sums, so
-  // that enough bytes are in flight for this pure-bandwidth pass.
+  // lanes (2 at D = 128 in 16 bits) and every thread issues the loads of four passes before it sums, so that
+  // enough bytes are in flight for this pure-bandwidth pass.
   const int vpr = D / VE;                              // vectors per row (1 .. 32)
   const int rpw = 32 / vpr;                            // rows per warp and pass
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -98,27 +98,33 @@ bwd_prep_kernel(const T* __restrict__ dout, const Strides do_str, const T* __res
   const int ih = blockIdx.y, ib = blockIdx.z;
   const size_t bh = (size_t)ib * Hq + ih;
   const int row0 = blockIdx.x * 64;
-  // rows of this CTA: 64; warp w takes rows row0 + w*8 .. +8 in passes of rpw rows, two passes at a time
-  for (int base = 0; base < 8; base += 2 * rpw) {
-    int r[2];
-    float s[2] = {0.f, 0.f};
-    float a[2][VE], b2[2][VE];
-    bool live[2];
+  // rows of this CTA: 64; warp w takes rows row0 + w*8 .. +8 in passes of rpw rows, kInFlight passes at a time:
+  // the raw 16-byte vectors of all of them are requested before the first is summed (128 bytes per thread)
+  constexpr int kInFlight = 4;
+  for (int base = 0; base < 8; base += kInFlight * rpw) {
+    int r[kInFlight];
+    float s[kInFlight];
+    uint4 a[kInFlight], b2[kInFlight];
+    bool live[kInFlight];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < kInFlight; ++k) {
       const int in_warp = base + k * rpw + sub;        // 0 .. 7 when live
       r[k] = row0 + warp * 8 + in_warp;
       live[k] = sub < rpw && in_warp < 8 && r[k] < Sq;
+      s[k] = 0.f;
       if (live[k]) {
-        load_vec16<T>(dout + do_str.at(ib, ih, r[k]) + c, a[k]);
-        load_vec16<T>(o + o_str.at(ib, ih, r[k]) + c, b2[k]);
+        a[k] = __ldg(reinterpret_cast<const uint4*>(dout + do_str.at(ib, ih, r[k]) + c));
+        b2[k] = __ldg(reinterpret_cast<const uint4*>(o + o_str.at(ib, ih, r[k]) + c));
       }
     }
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < kInFlight; ++k) {
       if (live[k]) {
+        float fa[VE], fb[VE];
+        unpack_vec16<T>(a[k], fa);
+        unpack_vec16<T>(b2[k], fb);
 #pragma unroll
-        for (int i = 0; i < VE; ++i) s[k] += a[k][i] * b2[k][i];
+        for (int i = 0; i < VE; ++i) s[k] += fa[i] * fb[i];
       }
       // sum over the vpr lanes of the row: lanes [sub*vpr, sub*vpr + vpr)
       for (int off = 1; off < vpr; off <<= 1) {
