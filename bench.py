@@ -303,7 +303,9 @@ def run_native(args):
                      "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(name),
                      "peak_source": f"{peaks['src']} ({'copy bandwidth' if is_decode else ('bf16 sustained' if long_region else 'bf16 burst')})",
                      "frac_of_burst": None if is_decode else achieved / peaks["tf"],
-                     "frac_of_sustained": None if is_decode else achieved / peaks["tf_sus"]},
+                     "frac_of_sustained": None if is_decode else achieved / peaks["tf_sus"],
+                     # nominal B200 figures, for context: 8 TB/s HBM3e, 2250 TFLOP/s dense bf16
+                     "frac_of_nominal": achieved / (8000.0 if is_decode else 2250.0)},
         "clocks": r["clocks"], "gpu_launches": r["launches"],
     }
     if r["e2e"] is not None:
