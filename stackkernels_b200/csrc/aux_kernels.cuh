@@ -36,7 +36,7 @@ rope_kernel(const T* __restrict__ x, const TT* __restrict__ cos_t, const TT* __r
             int S, int H, int D, int start_pos, int backward, int out_bhsd, long long n_rows, int pos_per_cta,
             int cta_per_pos) {
   constexpr int VE = Vec16<T>::N;
-  extern __shared__ float s_table[];                 // per staged position: cos row [0, D), sin row [D, 2D)
+  extern __shared__ __align__(16) float s_table[];                 // per staged position: cos row [0, D), sin row [D, 2D)
   const int half = D / 2;
   const int vph = half / VE;                         // vectors per half row (<= 256)
   const int tid = threadIdx.x;
@@ -110,12 +110,22 @@ rope_kernel(const T* __restrict__ x, const TT* __restrict__ cos_t, const TT* __r
     unpack_vec16<T>(r2[u], x2);
     T o1[VE], o2[VE];
 #pragma unroll
-    for (int e = 0; e < VE; ++e) {
-      const float c1 = tab[c + e], c2 = tab[half + c + e];
-      const float s1 = tab[D + c + e], s2 = tab[D + half + c + e];
-      // rot[:half] = -x2, rot[half:] = x1
-      o1[e] = from_f<T>(x1[e] * c1 + sg * (-x2[e]) * s1);
-      o2[e] = from_f<T>(x2[e] * c2 + sg * x1[e] * s2);
+    for (int e0 = 0; e0 < VE; e0 += 4) {
+      // 16-byte shared-memory reads: c, half and D are multiples of 4 floats (scalar reads made the kernel wait
+      // on the shared-memory instruction queue)
+      const float4 c1 = *reinterpret_cast<const float4*>(tab + c + e0);
+      const float4 c2 = *reinterpret_cast<const float4*>(tab + half + c + e0);
+      const float4 s1 = *reinterpret_cast<const float4*>(tab + D + c + e0);
+      const float4 s2 = *reinterpret_cast<const float4*>(tab + D + half + c + e0);
+      const float c1v[4] = {c1.x, c1.y, c1.z, c1.w}, c2v[4] = {c2.x, c2.y, c2.z, c2.w};
+      const float s1v[4] = {s1.x, s1.y, s1.z, s1.w}, s2v[4] = {s2.x, s2.y, s2.z, s2.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int e = e0 + i;
+        // rot[:half] = -x2, rot[half:] = x1
+        o1[e] = from_f<T>(x1[e] * c1v[i] + sg * (-x2[e]) * s1v[i]);
+        o2[e] = from_f<T>(x2[e] * c2v[i] + sg * x1[e] * s2v[i]);
+      }
     }
     size_t orow = (size_t)(row0 + lr);
     if (out_bhsd) {
