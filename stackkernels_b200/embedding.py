@@ -9,7 +9,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from .launchers import _DTYPES, _raise_for_status, _stream
+from .launchers import _DTYPES, _on_device, _raise_for_status, _stream
 
 
 def precompute_freqs(dim: int, max_seq_len: int = 4096, base: float = 10000.0, device="cpu",
@@ -39,7 +39,7 @@ def rope_launch(x, cos, sin, start_pos: int = 0, backward: bool = False, out_bhs
     cos = cos.to(device=x.device, dtype=tdt).contiguous()
     sin = sin.to(device=x.device, dtype=tdt).contiguous()
     out = torch.empty((B, H, S, D) if out_bhsd else (B, S, H, D), dtype=x.dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x):
         rc = _lib.load().skb_rope(x.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), B, S, H, D,
                                   _DTYPES[x.dtype], _DTYPES[tdt], int(start_pos), int(cos.shape[0]), int(backward),
                                   int(out_bhsd), _stream(x))
@@ -106,7 +106,7 @@ def kv_cache_append(k_cache, v_cache, k_new, v_new, cache_seqlens=None, start_po
         if cache_seqlens.dtype != torch.int32 or not cache_seqlens.is_cuda or tuple(cache_seqlens.shape) != (B,):
             raise ValueError(f"cache_seqlens must be an int32 CUDA tensor of shape ({B},)")
         lens_ptr = cache_seqlens.data_ptr()
-    with torch.cuda.device(k_cache.device):
+    with _on_device(k_cache):
         rc = _lib.load().skb_kv_append(k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), lens_ptr,
                                        int(start_pos or 0), int(advance), B, Hkv, k_new.shape[2], cap, D,
                                        _DTYPES[k_cache.dtype], _stream(k_cache))

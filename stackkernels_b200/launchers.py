@@ -9,6 +9,7 @@ C ABI of ``libskb200.so`` on torch's current CUDA stream.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import math
 
@@ -64,8 +65,38 @@ def _raise_for_status(rc: int, what: str):
     raise ValueError(msg)
 
 
+def _device_index(t) -> int:
+    idx = t.device.index
+    return torch.cuda.current_device() if idx is None else idx
+
+
 def _stream(t):
-    return torch.cuda.current_stream(t.device).cuda_stream
+    """Raw handle of torch's current stream on ``t``'s device.  (Building a ``torch.cuda.Stream`` object per call
+    costs ~6 us of host time, a quarter of a decode call; the raw accessor is what torch's own launchers use.)"""
+    try:
+        return torch._C._cuda_getCurrentRawStream(_device_index(t))
+    except AttributeError:
+        return torch.cuda.current_stream(t.device).cuda_stream
+
+
+_SAME_DEVICE = contextlib.nullcontext()
+
+
+def _on_device(t):
+    """Context that makes ``t``'s device current for the C call; nothing to do when it already is."""
+    idx = _device_index(t)
+    return _SAME_DEVICE if idx == torch.cuda.current_device() else torch.cuda.device(idx)
+
+
+_SM_COUNT: dict = {}
+
+
+def _sm_count(t) -> int:
+    idx = _device_index(t)
+    n = _SM_COUNT.get(idx)
+    if n is None:
+        n = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
 
 
 def _addressable(t) -> bool:
@@ -106,7 +137,7 @@ def flash_attn_fwd(q, k, v, is_causal=False, sm_scale=None, impl="auto", out=Non
     dense = all(t.is_contiguous() for t in (q, k, v)) and (out is None or out.is_contiguous())
     if not dense and all(_addressable(t) for t in (q, k, v)) and (out is None or _addressable(out)):
         o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=q.device)
-        with torch.cuda.device(q.device):
+        with _on_device(q):
             rc = lib.skb_attn_fwd_strided(q.data_ptr(), _strides3(q), k.data_ptr(), _strides3(k), v.data_ptr(),
                                           _strides3(v), o.data_ptr(), _strides3(o), lse.data_ptr(),
                                           B, H_q, H_kv, S_q, S_k, D, dt, int(bool(is_causal)), float(sm_scale),
@@ -117,7 +148,7 @@ def flash_attn_fwd(q, k, v, is_causal=False, sm_scale=None, impl="auto", out=Non
     # contiguous path (the reference's): copy what is not contiguous
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     o = out if out is not None and out.is_contiguous() else torch.empty(q.shape, dtype=q.dtype, device=q.device)
-    with torch.cuda.device(q.device):
+    with _on_device(q):
         rc = lib.skb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
                               B, H_q, H_kv, S_q, S_k, D, dt, int(bool(is_causal)), float(sm_scale),
                               impl_id, _stream(q))
@@ -148,7 +179,7 @@ def flash_attn_bwd(do, q, k, v, out, lse, is_causal=False, sm_scale=None, impl="
     if not all(t.is_contiguous() for t in ins) and all(_addressable(t) for t in ins):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)   # keep dense permuted layouts
         if all(_addressable(t) for t in (dq, dk, dv)):
-            with torch.cuda.device(q.device):
+            with _on_device(q):
                 rc = lib.skb_attn_bwd_strided(do.data_ptr(), _strides3(do), q.data_ptr(), _strides3(q), k.data_ptr(),
                                               _strides3(k), v.data_ptr(), _strides3(v), out.data_ptr(), _strides3(out),
                                               lse.data_ptr(), dq.data_ptr(), _strides3(dq), dk.data_ptr(), _strides3(dk),
@@ -160,7 +191,7 @@ def flash_attn_bwd(do, q, k, v, out, lse, is_causal=False, sm_scale=None, impl="
                 return dq, dk, dv
     do, q, k, v, out = (t.contiguous() for t in ins)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    with torch.cuda.device(q.device):
+    with _on_device(q):
         rc = lib.skb_attn_bwd(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                               dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H_q, H_kv, S_q, S_k, D, dt,
                               int(bool(is_causal)), float(sm_scale), impl_id, ws.data_ptr(), ws_bytes, _stream(q))
@@ -189,12 +220,12 @@ def flash_decode(q, k, v, sm_scale=None, cache_seqlens=None, return_lse=False, n
     lib = _lib.load()
     impl_id = _lib.IMPL_BY_NAME[impl]
     if num_splits <= 0:
-        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+        sms = _sm_count(q)
         num_splits = lib.skb_decode_num_splits(B, H_q, H_kv, S_k, D, dt, sms)
     ws_bytes = lib.skb_decode_workspace_bytes(B, H_q, H_kv, S_k, D, dt, num_splits)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
     if not all(t.is_contiguous() for t in (q, k, v)) and all(_addressable(t) for t in (q, k, v)):
-        with torch.cuda.device(q.device):
+        with _on_device(q):
             rc = lib.skb_decode_strided(q.data_ptr(), _strides3(q), k.data_ptr(), _strides3(k), v.data_ptr(),
                                         _strides3(v), lens_ptr, out.data_ptr(), _strides3(out), lse.data_ptr(),
                                         B, H_q, H_kv, S_k, D, dt, float(sm_scale), int(num_splits), impl_id,
@@ -203,7 +234,7 @@ def flash_decode(q, k, v, sm_scale=None, cache_seqlens=None, return_lse=False, n
             _raise_for_status(rc, "flash_decode")
             return (out, lse) if return_lse else out
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    with torch.cuda.device(q.device):
+    with _on_device(q):
         rc = lib.skb_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), lens_ptr, out.data_ptr(), lse.data_ptr(),
                             B, H_q, H_kv, S_k, D, dt, float(sm_scale), int(num_splits), impl_id,
                             ws.data_ptr(), ws_bytes, _stream(q))
@@ -248,11 +279,11 @@ def flash_decode_paged(q, k_pages, v_pages, block_table, cache_seqlens, sm_scale
     lib = _lib.load()
     cap = max_pages * page_size
     if num_splits <= 0:
-        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+        sms = _sm_count(q)
         num_splits = lib.skb_decode_num_splits(B, H_q, H_kv, cap, D, dt, sms)
     ws_bytes = lib.skb_decode_workspace_bytes(B, H_q, H_kv, cap, D, dt, num_splits)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-    with torch.cuda.device(q.device):
+    with _on_device(q):
         rc = lib.skb_decode_paged(q.data_ptr(), _strides3(q), k_pages.data_ptr(), _strides3(k_pages), v_pages.data_ptr(),
                                   _strides3(v_pages), block_table.data_ptr(), max_pages, cache_seqlens.data_ptr(),
                                   out.data_ptr(), _strides3(out), lse.data_ptr(), B, H_q, H_kv, num_pages, page_size, D,

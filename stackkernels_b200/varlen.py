@@ -15,7 +15,7 @@ import math
 import torch
 
 from . import _lib
-from .launchers import _addressable, _check_device_dtype, _raise_for_status, _stream
+from .launchers import _addressable, _check_device_dtype, _on_device, _raise_for_status, _stream
 
 
 def _strides2(t):
@@ -61,7 +61,7 @@ def flash_attn_varlen_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max
     cu_q, cu_k = _cu(cu_seqlens_q, q.device), _cu(cu_seqlens_k, q.device)
     out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lse = torch.empty((H_q, total_q), dtype=torch.float32, device=q.device)
-    with torch.cuda.device(q.device):
+    with _on_device(q):
         rc = _lib.load().skb_attn_fwd_varlen(
             q.data_ptr(), _strides2(q), k.data_ptr(), _strides2(k), v.data_ptr(), _strides2(v), out.data_ptr(),
             _strides2(out), lse.data_ptr(), cu_q.data_ptr(), cu_k.data_ptr(), B, H_q, H_kv, total_q, total_k,
@@ -92,7 +92,7 @@ def flash_attn_varlen_bwd(do, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max
     lib = _lib.load()
     ws_bytes = lib.skb_attn_bwd_varlen_workspace_bytes(B, H_q, total_q, D)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-    with torch.cuda.device(q.device):
+    with _on_device(q):
         rc = lib.skb_attn_bwd_varlen(
             do.data_ptr(), _strides2(do), q.data_ptr(), _strides2(q), k.data_ptr(), _strides2(k), v.data_ptr(),
             _strides2(v), out.data_ptr(), _strides2(out), lse.data_ptr(), dq.data_ptr(), _strides2(dq), dk.data_ptr(),
